@@ -1,0 +1,412 @@
+#!/usr/bin/env python
+"""Headline benchmark: packed-KV decode attention, one layer, Llama-3.1-8B shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--batch B] [--ctx C] [--page P] [--splits S] [--stat fp16|bf16]
+
+A *step* is one pass of the hot path over one decode batch: fused paged split-KV
+attention of one query token per request over its packed 4-bit cache (+ the
+log-sum-exp combine).  Default workload (N=1): batch 64, 32 query / 8 KV heads,
+head_dim 128, context 8192, 16-token pages, random block table, bf16 queries; the
+cache holds real codes produced by the encode-on-write kernel from N(0,1) K/V with
+four K outlier channels per head scaled by 8.
+
+``value``  : packed-cache bytes attended per second (5 effective bits per scalar:
+             seq_len * Hkv * 160 B per request), all ranks, inputs resident in HBM.
+``e2e``    : the same metric for the full serving step through the public API with
+             HOST inputs: pinned q / new-token K,V / slots / seq_lens -> device,
+             encode-on-write of the new token, decode attention, output -> host.
+N > 1 (torchrun): every rank owns its own batch and page pool (request-batch
+sharding, no collective on the data path); time is the max over ranks.
+
+``--impl reference`` times the CPU implementation of the same path (numpy port of
+the reference's eager-PyTorch exact-mode attention) on the host cores, on a bounded
+sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+HEADS_Q, HEADS_KV, HEAD_DIM = 32, 8, 128
+BYTES_PER_TOKEN_HEAD = 160  # 64 B K codes + 16 B K stats + 64 B V codes + 16 B V stats
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--splits", type=int, default=0, help="0 = launch policy")
+    ap.add_argument("--stat", default="fp16", choices=["fp16", "bf16"])
+    ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 CUDA-core kernel, 2 tensor-core kernel")
+    ap.add_argument("--cpu-sample-requests", type=int, default=0, help="0 = one per host core")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dense-baseline", action="store_true", help="also time the bf16-KV kernel on the same shapes")
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def ncu_traffic_bytes(workload: str):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
+    path = os.path.join(REPO, "beyond-kv-cache_b200", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f).get(workload)
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_decode_baseline(args, sample_requests: int, steps: int = 1, warmup: int = 0):
+    """The oracle's decode path on the host cores (see oracle/cpu_bench.py)."""
+    from beyond_kv_cache_b200 import synth
+    from oracle.cpu_bench import time_decode_sample
+
+    lk, tk = synth.make_tables(HEADS_KV, seed=0, which="k")
+    lv, tv = synth.make_tables(HEADS_KV, seed=0, which="v")
+    tabs = tuple(t.float().numpy() for t in (lk, tk, lv, tv))
+    cores = os.cpu_count() or 1
+    requests = sample_requests or cores
+    secs, workers, nbytes = time_decode_sample(
+        requests=requests, ctx=args.ctx, heads_kv=HEADS_KV, heads_q=HEADS_Q, block_size=args.page, tables=tabs,
+        stat="f16" if args.stat == "fp16" else "bf16", steps=steps, warmup=warmup, workers=cores)
+    return {
+        "value": nbytes / secs / 1e9,
+        "unit": "GB/s",
+        "cores": workers,
+        "kind": "port",
+        "sample": f"{requests} of the batch's requests x ctx {args.ctx}, one decode step each, numpy float64 "
+                  f"attention over the packed pages, {workers} worker processes",
+        "seconds_per_step": secs,
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    warm = 1 if args.warmup > 0 else 0
+    base = cpu_decode_baseline(args, args.cpu_sample_requests, steps=steps, warmup=warm)
+    line = {
+        "impl": "reference",
+        "metric": "packed_kv_decode_attention_throughput",
+        "value": base["value"],
+        "unit": "GB/s",
+        "n_gpus": args.gpus,
+        "steps": steps,
+        "warmup": warm,
+        "ms_per_step": base["seconds_per_step"] * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f64",
+        "data": "synthetic",
+        "config": workload_config(args, note="bounded CPU sample: " + base["sample"]),
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, note: str | None = None):
+    cfg = {
+        "workload": f"llama-3.1-8b-shaped single-layer decode: batch {args.batch}/GPU x ctx {args.ctx}, "
+                    f"{HEADS_Q} q / {HEADS_KV} kv heads, head_dim {HEAD_DIM}, {args.page}-token pages, random block table",
+        "batch_per_gpu": args.batch,
+        "context": args.ctx,
+        "page_tokens": args.page,
+        "stat_dtype": args.stat,
+        "query_dtype": "bf16",
+        "l2_policy": "inputs larger than L2 (packed cache >> 126 MB), no flush",
+        "sharding": "request batch per GPU, no data-path collective",
+    }
+    if note:
+        cfg["note"] = note
+    return cfg
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from beyond_kv_cache_b200 import _lib, synth
+    from beyond_kv_cache_b200.quant.beyond_cute import PagedLayout, write_tokens_to_paged_cache
+    from beyond_kv_cache_b200.quant.fa4_cute import beyond_mixed_decode_runtime as rt
+
+    _lib.load()  # fail loudly when the CUDA library is missing
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path for the product")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, ctx, BS = args.batch, args.ctx, args.page
+    stat_dtype = torch.float16 if args.stat == "fp16" else torch.bfloat16
+    layout = PagedLayout.build_hnd(BS, HEADS_KV, HEAD_DIM, 4, 32, 32)
+    pages_per_seq = (ctx + BS - 1) // BS + 1  # room for the appended tokens of the e2e steps
+    block_table, num_pages = synth.random_block_table(B, pages_per_seq, seed=rank, device=dev)
+    cache = torch.zeros((num_pages, layout.block_i32), dtype=torch.int32, device=dev)
+    lk, tk = (t.to(dev) for t in synth.make_tables(HEADS_KV, seed=0, which="k"))
+    lv, tv = (t.to(dev) for t in synth.make_tables(HEADS_KV, seed=0, which="v"))
+
+    # ---- fill the cache with real codes through the encode-on-write kernel (untimed) ----
+    chunk = 2048
+    for start in range(0, ctx, chunk):
+        n = min(chunk, ctx - start)
+        k, v = synth.make_kv(B * n, HEADS_KV, seed=1000 * rank + start, device=dev)
+        slots = synth.slots_for(block_table, BS, start, n)
+        write_tokens_to_paged_cache(cache, layout, block_table, slots, k, v, q_points_k=lk, q_points_v=lv,
+                                    thresholds_k=tk, thresholds_v=tv, require_fast=True, stat_dtype=stat_dtype)
+    del k, v
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77 + rank)
+    q = torch.randn((B, HEADS_Q, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
+    seq_lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+    out = torch.empty_like(q)
+    max_seq_len = pages_per_seq * BS
+    rk, rv = rt.prepare_runtime_qpoints(lk, lv, heads_kv=HEADS_KV)
+    spec = rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=block_table, heads_q=HEADS_Q,
+                                max_seq_len=max_seq_len, num_splits=args.splits)
+    ws = rt.allocate_runtime_workspace(spec, device=dev)
+    scale = synth.softmax_scale()
+
+    def decode_step():
+        rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=block_table,
+                                 seq_lens=seq_lens, k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
+                                 workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(max(args.warmup, 3)):
+        decode_step()
+    sync_all()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        decode_step()
+    ev1.record()
+    sync_all()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = ms_total / args.steps
+    packed_bytes = B * ctx * HEADS_KV * BYTES_PER_TOKEN_HEAD  # per rank per step
+    value = world * packed_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end-to-end serving step with host inputs --------------------------------------
+    e2e_steps = args.steps
+    h_q = torch.randn((B, HEADS_Q, HEAD_DIM)).to(torch.bfloat16).pin_memory()
+    h_k = torch.randn((B, HEADS_KV, HEAD_DIM)).to(torch.bfloat16).pin_memory()
+    h_v = torch.randn((B, HEADS_KV, HEAD_DIM)).to(torch.bfloat16).pin_memory()
+    h_out = torch.empty((B, HEADS_Q, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
+    bt_cpu = block_table.cpu()
+    h_lens = torch.empty((B,), dtype=torch.int32).pin_memory()
+    h_slots = torch.empty((B,), dtype=torch.int32).pin_memory()
+    d_q, d_k, d_v = torch.empty_like(q), torch.empty((B, HEADS_KV, HEAD_DIM), dtype=torch.bfloat16, device=dev), None
+    d_v = torch.empty_like(d_k)
+    d_lens = torch.empty((B,), dtype=torch.int32, device=dev)
+    d_slots = torch.empty((B,), dtype=torch.int32, device=dev)
+    spare = BS  # tokens of head-room in the last page
+
+    def e2e_step(i: int):
+        pos = ctx + (i % spare)  # position of the appended token
+        h_lens.fill_(pos + 1)
+        h_slots.copy_(bt_cpu[:, pos // BS] * BS + pos % BS)
+        d_q.copy_(h_q, non_blocking=True)
+        d_k.copy_(h_k, non_blocking=True)
+        d_v.copy_(h_v, non_blocking=True)
+        d_lens.copy_(h_lens, non_blocking=True)
+        d_slots.copy_(h_slots, non_blocking=True)
+        write_tokens_to_paged_cache(cache, layout, block_table, d_slots, d_k, d_v, q_points_k=lk, q_points_v=lv,
+                                    thresholds_k=tk, thresholds_v=tv, require_fast=True, stat_dtype=stat_dtype)
+        rt.run_nonuniform_decode(spec=spec, q=d_q, cache=cache, layout=layout, block_table=block_table,
+                                 seq_lens=d_lens, k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
+                                 workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
+        h_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller needs the result of this step
+
+    for i in range(3):
+        e2e_step(i)
+    sync_all()
+    t0 = time.perf_counter()
+    ev0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    ev1.record()
+    sync_all()
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max_over_ranks(max(ev0.elapsed_time(ev1), 0.0)) / e2e_steps
+    h2d = (h_q.numel() + h_k.numel() + h_v.numel()) * 2 + (h_lens.numel() + h_slots.numel()) * 4
+    d2h = h_out.numel() * 2
+    e2e_value = world * packed_bytes / (e2e_ms * 1e-3) / 1e9
+
+    dense = None
+    if args.dense_baseline and rank == 0:
+        dense = time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, spec.num_splits, scale, args)
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        achieved = packed_bytes / (ms_per_step * 1e-3) / 1e9  # one GPU, one launch of the dominant kernel
+        workload_key = f"decode_b{B}_ctx{ctx}_p{BS}"
+        line = {
+            "metric": "packed_kv_decode_attention_throughput",
+            "value": value,
+            "unit": "GB/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step,
+            "us_per_layer": ms_per_step * 1e3,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f16 tensor-core operands, f32 accumulate" if args.variant != 1 else "f32",
+            "data": "synthetic",
+            "config": dict(workload_config(args), num_splits=spec.num_splits, kernel_variant=args.variant),
+            "roofline": {
+                "bound": "hbm",
+                "achieved": achieved,
+                "peak": peak,
+                "unit": "GB/s",
+                "frac": achieved / peak,
+                "peak_source": f"{peak_kind} copy bandwidth",
+                "algorithmic_bytes_per_launch": packed_bytes,
+                "traffic": ncu_traffic_bytes(workload_key),
+                "note": "duration is the whole step (decode kernel + combine kernel when split)",
+            },
+            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps * (2 if spec.num_splits > 1 else 1),
+            "clocks": clocks,
+        }
+        if dense is not None:
+            line["dense_kv_baseline"] = dense
+        if world == 1 and not args.no_cpu_baseline:
+            base = cpu_decode_baseline(args, args.cpu_sample_requests)
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, splits, scale, args):
+    """bf16-KV decode attention on the same shapes and block table (512 B per token-head)."""
+    num_pages = int(block_table.max().item()) + 1
+    k_pages = torch.randn((num_pages, BS, HEADS_KV, HEAD_DIM), device=dev).to(torch.bfloat16)
+    v_pages = torch.randn((num_pages, BS, HEADS_KV, HEAD_DIM), device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    seq_lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+    o = torch.empty((splits, B, HEADS_Q, HEAD_DIM), dtype=torch.float32, device=dev)
+    m = torch.empty((splits, B, HEADS_Q), dtype=torch.float32, device=dev)
+    l = torch.empty_like(m)
+
+    def step():
+        _lib.call("bkv_decode_dense_sm100", q.data_ptr(), q.stride(0), _lib.BKV_BF16, k_pages.data_ptr(),
+                  v_pages.data_ptr(), _lib.BKV_BF16, num_pages, BS, HEADS_KV, block_table.data_ptr(),
+                  block_table.stride(0), seq_lens.data_ptr(), out.data_ptr(), _lib.BKV_BF16, o.data_ptr(),
+                  m.data_ptr(), l.data_ptr(), splits, B, HEADS_Q, block_table.shape[1] * BS, scale,
+                  _lib.current_stream(dev))
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    nbytes = B * ctx * HEADS_KV * 512
+    return {"us_per_layer": ms * 1e3, "GBps_bf16_bytes": nbytes / (ms * 1e-3) / 1e9, "bytes_per_token_head": 512}
+
+
+if __name__ == "__main__":
+    main()

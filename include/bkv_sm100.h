@@ -1,0 +1,179 @@
+/*
+ * bkv_sm100.h — C ABI of the B200 (sm_100a) packed-KV hot path.
+ *
+ * One shared library, libbkv_sm100.so, exports the entry points below.  They take
+ * raw device pointers, sizes, element strides and a CUDA stream handle; they never
+ * allocate, never synchronise and never throw: every call returns BKV_OK or a
+ * negative status (see bkv_status_string).  Launch errors reported by the CUDA
+ * runtime are returned as BKV_ERR_CUDA and the message is kept per thread
+ * (bkv_last_cuda_error).
+ *
+ * Every entry point names the reference interface (wsxhjnb1/Beyond-KV-Cache,
+ * path:line inside that project) that it replaces.
+ *
+ * Packed page ABI (identical to the reference, quant/beyond_cute.py:675-765):
+ * the cache is `int32 [num_pages][page_stride_i32]`; one page holds, in order,
+ * K codes, K statistics, V codes, V statistics for `block_size` tokens and
+ * `heads_kv` heads of 128 scalars each, quantised in groups of 32 to 4-bit codes
+ * (8 codes per 32-bit word, code i in bits 4*(i%8)) with one statistics word per
+ * group (low 16 bits = scale, high 16 bits = minimum, both fp16 or bf16).
+ */
+#ifndef BKV_SM100_H_
+#define BKV_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BKV_ABI_VERSION 1
+
+/* status codes */
+#define BKV_OK 0
+#define BKV_ERR_ARG (-1)         /* null pointer / negative size / bad enum          */
+#define BKV_ERR_UNSUPPORTED (-2) /* a shape or layout this library does not handle   */
+#define BKV_ERR_ALIGN (-3)       /* pointer or stride not aligned as documented      */
+#define BKV_ERR_CUDA (-4)        /* CUDA runtime reported an error at launch         */
+#define BKV_ERR_LIMIT (-5)       /* size beyond a documented maximum                 */
+
+/* element types */
+#define BKV_F16 0
+#define BKV_BF16 1
+#define BKV_F32 2
+
+/* code layouts of the page (quant/beyond_cute.py:56-58) */
+#define BKV_LAYOUT_HEAD_WORD_TOKEN 1 /* ABI v1: word-major, token-minor */
+#define BKV_LAYOUT_HND_TOKEN_WORD 2  /* ABI v2: token-major (production) */
+
+/* flags */
+#define BKV_FLAG_PDL_TRIGGER 0x1   /* encode: signal dependent launch early          */
+#define BKV_FLAG_PDL_WAIT 0x2      /* decode: wait for the preceding kernel (PDL)    */
+#define BKV_FLAG_LINEAR_SEARCH 0x4 /* encode: count thresholds linearly (unsorted tables) */
+#define BKV_FLAG_KLEVELS_LANE_MAJOR 0x8 /* decode: K levels given as (Hkv,16,4)      */
+
+typedef void* bkv_stream_t; /* a cudaStream_t / CUstream */
+
+int bkv_abi_version(void);
+const char* bkv_status_string(int status);
+const char* bkv_last_cuda_error(void);
+
+/*
+ * Encode-on-write.  Replaces write_tokens_to_paged_cache ->
+ * _try_write_tokens_to_paged_cache_triton -> _write_packed_kv_cache_group_head128_kernel
+ * (quant/beyond_cute.py:2147-2207, :1556-1700, :934-1164); bit-exact with the
+ * reference quantiser quantize_k / quantize_v (:439-486, :525-584).
+ *
+ * k, v ........ [num_tokens][heads_kv][128] of in_dtype, innermost stride 1,
+ *               token/head strides in elements; rows 16-byte aligned.
+ * slots ....... int32 or int64 flat slot ids (page*block_size + offset); a
+ *               negative slot writes nothing to the cache.
+ * thr_*, lvl_*  15 thresholds / 16 levels of table_dtype, either one shared table
+ *               (grouped_* = 0) or heads_kv*4 tables indexed head*4+group.
+ * k_dq, v_dq .. optional (may be NULL, may alias k / v): reconstruction
+ *               level*stored_scale + stored_min rounded to in_dtype
+ *               (reference :1042-1079), written for every row, also slot < 0.
+ */
+int bkv_encode_sm100(const void* k, const void* v, int64_t k_stride_t, int64_t k_stride_h,
+                     int64_t v_stride_t, int64_t v_stride_h, int in_dtype, const void* slots,
+                     int slot_is_i64, int64_t slot_stride, int64_t num_tokens, int heads_kv,
+                     void* cache, int64_t num_pages, int64_t page_stride_i32, int block_size,
+                     int code_layout, int stat_dtype, const void* thr_k, const void* thr_v,
+                     const void* lvl_k, const void* lvl_v, int table_dtype, int grouped_k,
+                     int grouped_v, void* k_dq, void* v_dq, int64_t kdq_stride_t,
+                     int64_t kdq_stride_h, int64_t vdq_stride_t, int64_t vdq_stride_h, int flags,
+                     bkv_stream_t stream);
+
+/*
+ * Fused paged split-KV decode attention over the packed cache.  Replaces
+ * run_nonuniform_decode -> MixedInputFusedMultiHeadAttentionDecode (+ reducer)
+ * (quant/fa4_cute/beyond_mixed_decode_runtime.py:520-612,
+ *  quant/fa4_cute/beyond_mixed_decode_sm100.py:930-3214).
+ *
+ * q ............. [batch][heads_q][128] q_dtype, head stride 128, batch stride given.
+ * block_table ... int32 [batch][>= ceil(max seq_len / block_size)], row stride given.
+ * seq_lens ...... int32 [batch]; 0 gives a zero output row.
+ * lvl_k, lvl_v .. heads_kv*4 tables of 16 levels (table_dtype); K may be given in
+ *                 the launcher's (Hkv,16,4) order with BKV_FLAG_KLEVELS_LANE_MAJOR.
+ * out ........... [batch][heads_q][128] out_dtype, contiguous.
+ * out_f32 ....... optional float32 copy of the un-rounded result (may be NULL).
+ * o/m/l_partial . float32 workspaces [num_splits][batch][heads_q]([128]); only read
+ *                 and written when num_splits > 1.
+ * Split s of a request covers pages s, s+num_splits, ... of its block table row.
+ */
+int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const void* cache,
+                     int64_t num_pages, int64_t page_stride_i32, int block_size, int heads_kv,
+                     int stat_dtype, const int32_t* block_table, int64_t block_table_stride,
+                     const int32_t* seq_lens, const void* lvl_k, const void* lvl_v,
+                     int table_dtype, void* out, int out_dtype, float* out_f32, float* o_partial,
+                     float* m_partial, float* l_partial, int num_splits, int batch, int heads_q,
+                     int max_seq_len, float softmax_scale, int flags, int variant,
+                     bkv_stream_t stream);
+
+/*
+ * Log-sum-exp merge of split partials.  Replaces reduction_parallel_weights /
+ * reduction_cta4_weights / reduction_warp_parallel_weights
+ * (quant/fa4_cute/beyond_mixed_decode_sm100.py:2935-3214).  m_partial is in the
+ * natural-log domain of the scaled scores.  rows = batch*heads_q.
+ */
+int bkv_combine_sm100(const float* o_partial, const float* m_partial, const float* l_partial,
+                      int num_splits, int64_t rows, void* out, int out_dtype, float* out_f32,
+                      bkv_stream_t stream);
+
+/*
+ * Partial (un-normalised) decode over pages [page_lo, page_hi) of every request:
+ * writes o/m/l for ONE split slot; used for the KV-range split across GPUs, whose
+ * partials are exchanged and merged with bkv_combine_sm100.  No counterpart in the
+ * reference (it has no multi-GPU decode); the arithmetic is that of bkv_decode_sm100.
+ */
+int bkv_decode_range_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const void* cache,
+                           int64_t num_pages, int64_t page_stride_i32, int block_size,
+                           int heads_kv, int stat_dtype, const int32_t* block_table,
+                           int64_t block_table_stride, const int32_t* seq_lens, const void* lvl_k,
+                           const void* lvl_v, int table_dtype, float* o_partial, float* m_partial,
+                           float* l_partial, int batch, int heads_q, int token_lo, int token_hi,
+                           float softmax_scale, int flags, bkv_stream_t stream);
+
+/*
+ * Paged read-back to dense varlen K/V.  Replaces dequantize_paged_kv_to_dense and
+ * its two Triton kernels (quant/beyond_cute.py:1703-1856, :1166-1476); bit-exact
+ * with read_request_from_paged_cache (:2210-2395).
+ * out_k/out_v: [total_tokens][heads_kv][128] out_dtype, contiguous; request r
+ * writes rows seq_start[r] .. seq_start[r]+seq_lens[r]-1.
+ */
+int bkv_readback_sm100(const void* cache, int64_t num_pages, int64_t page_stride_i32,
+                       int block_size, int heads_kv, int stat_dtype, const int32_t* block_table,
+                       int64_t block_table_stride, int64_t block_table_width,
+                       const int32_t* seq_lens, const int32_t* seq_start, int batch,
+                       int max_seq_len, const void* lvl_k, const void* lvl_v, int table_dtype,
+                       int grouped_k, int grouped_v, void* out_k, void* out_v, int out_dtype,
+                       bkv_stream_t stream);
+
+/*
+ * bf16/fp16-KV paged decode attention of the same shape and split policy: the
+ * full-precision baseline the packed kernel is measured against.  K and V pages:
+ * [num_pages][block_size][heads_kv][128] kv_dtype.  No counterpart in the
+ * reference repository (it compares against FlashAttention-4).
+ */
+int bkv_decode_dense_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const void* k_pages,
+                           const void* v_pages, int kv_dtype, int64_t num_pages, int block_size,
+                           int heads_kv, const int32_t* block_table, int64_t block_table_stride,
+                           const int32_t* seq_lens, void* out, int out_dtype, float* o_partial,
+                           float* m_partial, float* l_partial, int num_splits, int batch,
+                           int heads_q, int max_seq_len, float softmax_scale,
+                           bkv_stream_t stream);
+
+/*
+ * Last-token slot derivation for graph-safe decode:
+ * slot[b] = block_table[b][(len-1)/BS]*BS + (len-1)%BS, or -1 when len <= 0 or the
+ * page id is negative.  Replaces _derive_dense_decode_slot_mapping_kernel
+ * (src/beyond/runtime/vllm/packed_backend.py:2251-2283).
+ */
+int bkv_derive_slots_sm100(const int32_t* seq_lens, const int32_t* block_table,
+                           int64_t block_table_stride, int64_t block_table_width, int block_size,
+                           int batch, int32_t* slots_out, bkv_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BKV_SM100_H_ */

@@ -1,0 +1,180 @@
+"""Packed decode attention parity: the CUDA path (through the launcher mirror and the
+C ABI) against the float64 oracle over the same packed pages.
+
+Tolerances (stated by the task): |out_f32 - oracle| <= 2e-3 on the un-rounded float32
+result; the bf16/fp16 output must be within one unit in the last place of the rounded
+oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from beyond_kv_cache_b200 import _lib, synth
+from beyond_kv_cache_b200.quant.beyond_cute import PagedLayout
+from tests.helpers import KIND_TO_DTYPE, gpu_decode, oracle_cache, tables
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL = 2e-3
+
+
+def _ulp(x: torch.Tensor, dtype) -> torch.Tensor:
+    """Spacing of `dtype` at |x| (normal range)."""
+    mant = 7 if dtype == torch.bfloat16 else 10
+    e = torch.floor(torch.log2(x.float().abs().clamp_min(2.0**-14)))
+    return torch.pow(2.0, e - mant)
+
+
+def _check_rounded(out: torch.Tensor, out32: torch.Tensor, want32: np.ndarray, err: float) -> None:
+    """The 16-bit output is the round-to-nearest of the kernel's own float32 result and
+    sits within one unit in the last place (plus the float32 error) of the rounded oracle."""
+    assert torch.equal(out, out32.to(out.dtype))
+    want = torch.from_numpy(want32).to(out.dtype)
+    gap = (out.float() - want.float()).abs()
+    assert bool((gap <= _ulp(want, out.dtype) + 2 * err).all())
+
+
+def _check(q, cache, bt, lens, heads_kv, bs, lk, lv, kind, **kw):
+    out, out32, spec = gpu_decode(q, cache, bt, lens, heads_kv, bs, lk, lv, kind=kind, **kw)
+    want = oracle.decode_attention(
+        q.float().numpy(), cache, oracle.PageGeometry(bs, heads_kv), bt, lens,
+        levels_k=lk.float().numpy(), levels_v=lv.float().numpy(), softmax_scale=synth.softmax_scale(), stat=kind,
+    )
+    err = float(np.abs(out32.numpy() - want).max())
+    assert err <= TOL, f"max-abs {err} > {TOL} (splits={spec.num_splits})"
+    _check_rounded(out, out32, want, err)
+    return err, spec
+
+
+@pytest.mark.parametrize("variant", [1, 0])
+def test_config0_against_reference_output(golden, variant):
+    """Config 0 (float32 Q, fp16 statistics): the numbers the reference's own code
+    produced (fp32 SDPA over its read-back cache), within 2e-3, straight through the
+    C ABI; then the bf16-query form through the launcher mirror against the oracle."""
+    g = golden["config0"]
+    q, k, v = synth.config0_inputs(0)
+    lk, tk, lv, tv = tables(8, 0, per_group=False)
+    geo = oracle.PageGeometry(16, 8)
+    bt = g["c0_block_table"]
+    slots = (bt.astype(np.int64)[:, np.arange(1024) // 16] * 16 + np.arange(1024) % 16).reshape(-1)
+    cache = np.zeros((256, geo.block_i32), dtype=np.int32)
+    oracle.write_pages(cache, geo, slots, k, v, thresholds_k=tk.float().numpy(), thresholds_v=tv.float().numpy(), stat="f16")
+    qd, cd, btd = torch.from_numpy(q).to(DEV), torch.from_numpy(cache).to(DEV), torch.from_numpy(bt).to(DEV)
+    lens = torch.full((4,), 1024, dtype=torch.int32, device=DEV)
+    lkd, lvd = lk.to(DEV), lv.to(DEV)
+    out = torch.empty((4, 32, 128), dtype=torch.float32, device=DEV)
+    for splits in (1, 4):
+        ws = [torch.empty((splits, 4, 32, 128), device=DEV), torch.empty((splits, 4, 32), device=DEV), torch.empty((splits, 4, 32), device=DEV)]
+        out.zero_()
+        _lib.call("bkv_decode_sm100", qd.data_ptr(), qd.stride(0), _lib.BKV_F32, cd.data_ptr(), cd.shape[0], cd.stride(0),
+                  16, 8, _lib.BKV_F16, btd.data_ptr(), btd.stride(0), lens.data_ptr(), lkd.data_ptr(), lvd.data_ptr(),
+                  _lib.BKV_F16, out.data_ptr(), _lib.BKV_F32, None, ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(),
+                  splits, 4, 32, 1024, synth.softmax_scale(), 0, variant, _lib.current_stream(qd.device))
+        torch.cuda.synchronize()
+        assert np.abs(out.cpu().numpy() - g["c0_out"]).max() <= TOL
+    qb = torch.from_numpy(q).to(torch.bfloat16)
+    _check(qb, cache, bt, [1024] * 4, 8, 16, lk, lv, "f16", variant=variant)
+
+
+@pytest.mark.parametrize("variant", [1, 0])
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("bs,gqa,heads_kv", [(16, 4, 8), (64, 4, 2), (128, 8, 2), (32, 2, 4), (16, 1, 4)])
+def test_ragged_batch(bs, gqa, heads_kv, kind, variant):
+    lens = [0, 1, bs - 1, bs, bs + 1, 5 * bs + 7, 333, 2]
+    lk, tk, lv, tv = tables(heads_kv, 21)
+    cache, bt = oracle_cache(lens, heads_kv, bs, kind, 77, tk.float().numpy(), tv.float().numpy())
+    rng = np.random.default_rng(9)
+    q = torch.from_numpy(rng.standard_normal((len(lens), heads_kv * gqa, 128)).astype(np.float32)).to(KIND_TO_DTYPE[kind])
+    for splits in (1, 3, 0):
+        _, spec = _check(q, cache, bt, lens, heads_kv, bs, lk, lv, kind, splits=splits, variant=variant)
+    out, out32, _ = gpu_decode(q, cache, bt, lens, heads_kv, bs, lk, lv, kind=kind, variant=variant)
+    assert not out[0].any() and not out32[0].any()  # seq_len 0 -> zeros
+
+
+@pytest.mark.parametrize("variant", [1, 0])
+def test_long_context_many_splits(variant):
+    lens = [16 * 1024 + 5, 9000]
+    lk, tk, lv, tv = tables(2, 3)
+    cache, bt = oracle_cache(lens, 2, 16, "bf16", 5, tk.float().numpy(), tv.float().numpy())
+    q = torch.from_numpy(np.random.default_rng(2).standard_normal((2, 8, 128)).astype(np.float32)).to(torch.bfloat16)
+    for splits in (1, 7, 32):
+        _check(q, cache, bt, lens, 2, 16, lk, lv, "bf16", splits=splits, variant=variant)
+
+
+def test_fused_qkv_query_view_and_bucket_truncation():
+    lens = [100, 40]
+    lk, tk, lv, tv = tables(2, 4)
+    cache, bt = oracle_cache(lens, 2, 16, "f16", 6, tk.float().numpy(), tv.float().numpy())
+    rng = np.random.default_rng(3)
+    fused = torch.from_numpy(rng.standard_normal((2, 8 + 4, 128)).astype(np.float32)).to(torch.float16)
+    q = fused[:, :8]  # batch stride 12*128
+    _check(q, cache, bt, lens, 2, 16, lk, lv, "f16", splits=2)
+    # a launch bucket shorter than a request attends only the bucket (reference semantics)
+    out, out32, _ = gpu_decode(q.contiguous(), cache, bt, lens, 2, 16, lk, lv, kind="f16", max_seq_len=64)
+    want = oracle.decode_attention(q.float().numpy(), cache, oracle.PageGeometry(16, 2), bt, [64, 40],
+                                   levels_k=lk.float().numpy(), levels_v=lv.float().numpy(),
+                                   softmax_scale=synth.softmax_scale(), stat="f16")
+    assert np.abs(out32.numpy() - want).max() <= TOL
+
+
+def test_kv_range_partials_merge_to_full():
+    """bkv_decode_range_sm100 over disjoint token ranges + bkv_combine_sm100 == full decode."""
+    lens = [700, 130, 0, 64]
+    lk, tk, lv, tv = tables(2, 8)
+    cache, bt = oracle_cache(lens, 2, 16, "bf16", 10, tk.float().numpy(), tv.float().numpy())
+    q = torch.from_numpy(np.random.default_rng(4).standard_normal((4, 8, 128)).astype(np.float32)).to(torch.bfloat16)
+    want = oracle.decode_attention(q.float().numpy(), cache, oracle.PageGeometry(16, 2), bt, lens,
+                                   levels_k=lk.float().numpy(), levels_v=lv.float().numpy(),
+                                   softmax_scale=synth.softmax_scale(), stat="bf16")
+    qd, cd, btd = q.to(DEV), torch.from_numpy(cache).to(DEV), torch.from_numpy(bt).to(DEV)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    lkd, lvd = lk.to(DEV), lv.to(DEV)
+    ranges = [(0, 256), (256, 512), (512, 768)]
+    o = torch.empty((len(ranges), 4, 8, 128), dtype=torch.float32, device=DEV)
+    m = torch.empty((len(ranges), 4, 8), dtype=torch.float32, device=DEV)
+    l = torch.empty_like(m)
+    stream = _lib.current_stream(qd.device)
+    for i, (lo, hi) in enumerate(ranges):
+        _lib.call("bkv_decode_range_sm100", qd.data_ptr(), qd.stride(0), _lib.BKV_BF16, cd.data_ptr(), cd.shape[0],
+                  cd.stride(0), 16, 2, _lib.BKV_BF16, btd.data_ptr(), btd.stride(0), lens_d.data_ptr(),
+                  lkd.data_ptr(), lvd.data_ptr(), _lib.BKV_F16, o[i].data_ptr(), m[i].data_ptr(), l[i].data_ptr(),
+                  4, 8, lo, hi, synth.softmax_scale(), 0, stream)
+    out = torch.empty((4, 8, 128), dtype=torch.float32, device=DEV)
+    _lib.call("bkv_combine_sm100", o.data_ptr(), m.data_ptr(), l.data_ptr(), len(ranges), 32, out.data_ptr(),
+              _lib.BKV_F32, None, stream)
+    torch.cuda.synchronize()
+    assert np.abs(out.cpu().numpy() - want).max() <= TOL
+    # the partials themselves agree with the oracle's partials after normalisation
+    po, pm, pl = oracle.decode_attention(q.float().numpy(), cache, oracle.PageGeometry(16, 2), bt, lens,
+                                         levels_k=lk.float().numpy(), levels_v=lv.float().numpy(),
+                                         softmax_scale=synth.softmax_scale(), stat="bf16",
+                                         kv_range=ranges[1], return_partials=True)
+    got = (o[1] / l[1].clamp_min(1e-30).unsqueeze(-1)).cpu().numpy()
+    ref = po / np.maximum(pl, 1e-30)[..., None]
+    live = pl > 0
+    assert np.abs(got[live] - ref[live]).max() <= TOL
+    assert not (l[1].cpu().numpy()[~live] != 0).any()
+
+
+def test_launcher_rejects_bad_contracts():
+    from beyond_kv_cache_b200.quant.fa4_cute import beyond_mixed_decode_runtime as rt
+
+    layout = PagedLayout.build_hnd(16, 2, 128, 4, 32, 32)
+    cache = torch.zeros((4, layout.block_i32), dtype=torch.int32, device=DEV)
+    bt = torch.zeros((1, 4), dtype=torch.int32, device=DEV)
+    q = torch.zeros((1, 8, 128), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError, match="multiple of page_size"):
+        rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=bt, heads_q=8, max_seq_len=20)
+    with pytest.raises(ValueError, match="block-table capacity"):
+        rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=bt, heads_q=8, max_seq_len=128)
+    with pytest.raises(ValueError, match="ABI v2"):
+        rt.make_runtime_spec(q=q, cache=cache, layout=PagedLayout.build(16, 2, 128, 4, 32, 32), block_table=bt, heads_q=8, max_seq_len=64)
+    with pytest.raises(ValueError, match="CUDA tensors"):
+        rt.make_runtime_spec(q=q.cpu(), cache=cache, layout=layout, block_table=bt, heads_q=8, max_seq_len=64)
+    spec = rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=bt, heads_q=8, max_seq_len=64, num_splits=2)
+    rk, rv = rt.prepare_runtime_qpoints(torch.rand(8, 16, device=DEV), torch.rand(8, 16, device=DEV), heads_kv=2)
+    with pytest.raises(ValueError, match="workspace"):
+        rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=bt,
+                                 seq_lens=torch.ones(1, dtype=torch.int32, device=DEV), k_qpoints_lane_major=rk,
+                                 v_qpoints_code_major=rv, out=torch.empty_like(q), workspace={}, softmax_scale=0.1)

@@ -1,0 +1,164 @@
+"""Encode-on-write parity: the CUDA writer against the oracle and the golden page
+bytes produced by the reference (bit-exact)."""
+
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from beyond_kv_cache_b200 import synth
+from beyond_kv_cache_b200.quant.beyond_cute import (
+    CODE_LAYOUT_HEAD_WORD_TOKEN,
+    CODE_LAYOUT_HND_TOKEN_WORD,
+    PagedLayout,
+    write_tokens_to_paged_cache,
+)
+from oracle.paged import ABI_TOKEN_MAJOR, ABI_WORD_MAJOR
+from tests.helpers import KIND_TO_DTYPE, bits16, tables
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("abi", ["v2", "v1"])
+@pytest.mark.parametrize("bs", [16, 64])
+def test_writer_matches_reference_bytes(golden, bs, abi, kind):
+    g = golden["writer"]
+    code_layout = CODE_LAYOUT_HND_TOKEN_WORD if abi == "v2" else CODE_LAYOUT_HEAD_WORD_TOKEN
+    layout = PagedLayout.build(bs, 2, 128, 4, 32, 32, code_layout=code_layout)
+    pages = 6 if bs == 16 else 2
+    seed_pages = np.random.default_rng(99).integers(-(2**31), 2**31, (pages, layout.block_i32)).astype(np.int32)
+    cache = torch.from_numpy(seed_pages).to(DEV)
+    dt = KIND_TO_DTYPE[kind]
+    k = torch.from_numpy(g["w_k32"]).to(dt).to(DEV)
+    v = torch.from_numpy(g["w_v32"]).to(dt).to(DEV)
+    k_in, v_in = k.clone(), v.clone()
+    tab = {n: torch.from_numpy(g[n]).to(torch.float16).to(DEV) for n in ("w_lv_k", "w_th_k", "w_lv_v", "w_th_v")}
+    slots = torch.from_numpy(g[f"w_slots_bs{bs}"]).to(DEV)
+    write_tokens_to_paged_cache(
+        cache, layout, torch.zeros((1, 1), dtype=torch.int32, device=DEV), slots, k, v,
+        q_points_k=tab["w_lv_k"], q_points_v=tab["w_lv_v"], thresholds_k=tab["w_th_k"], thresholds_v=tab["w_th_v"],
+        k_dq_out=k, v_dq_out=v, require_fast=True,
+    )
+    tag = f"bs{bs}_{abi}_{kind}"
+    assert np.array_equal(cache.cpu().numpy(), g[f"w_cache_{tag}"])
+    assert np.array_equal(bits16(k), g[f"w_kdq_bits_{tag}"])  # in place, slot -1 rows too
+    assert np.array_equal(bits16(v), g[f"w_vdq_bits_{tag}"])
+    assert not torch.equal(k, k_in) and not torch.equal(v, v_in)
+
+
+@pytest.mark.parametrize("case", ["ties_f16", "ties_bf16", "divrn"])
+def test_known_answer_vectors(golden, case):
+    g = golden["kat"]
+    kind = "bf16" if case.endswith("bf16") else "f16"
+    prefix = "divrn" if case == "divrn" else "ties"
+    x = torch.from_numpy(g[f"{case}_x"]).to(KIND_TO_DTYPE[kind]).reshape(1, 1, 128).to(DEV)
+    thr = torch.from_numpy(g[f"{prefix}_thresholds"]).to(torch.float16).to(DEV)
+    lv = torch.from_numpy(g[f"{prefix}_levels"]).to(torch.float16).to(DEV)
+    layout = PagedLayout.build_hnd(16, 1, 128, 4, 32, 32)
+    cache = torch.zeros((1, layout.block_i32), dtype=torch.int32, device=DEV)
+    write_tokens_to_paged_cache(
+        cache, layout, None, torch.tensor([3], dtype=torch.int32, device=DEV), x, x.clone(),
+        q_points_k=lv, q_points_v=lv, thresholds_k=thr, thresholds_v=thr, require_fast=True,
+    )
+    parts = oracle.paged.gather_request(cache.cpu().numpy(), oracle.PageGeometry(16, 1), [0], 4)
+    for which in ("k", "v"):
+        codes = oracle.unpack_nibbles(parts[f"{which}_words"])[3, 0]
+        assert np.array_equal(codes, g[f"{case}_codes"])
+        assert np.array_equal(parts[f"{which}_scale_bits"][3, 0], g[f"{case}_scale_bits"])
+        assert np.array_equal(parts[f"{which}_mn_bits"][3, 0], g[f"{case}_mn_bits"])
+    if case == "divrn":
+        assert int(oracle.unpack_nibbles(parts["k_words"])[3, 0, 0, 2]) == 11
+
+
+def test_config0_cache_checksum(golden):
+    """fp32 rows, fp16 statistics, 16-token pages, random block table: the whole cache
+    must hash to the value the reference's quantiser produced."""
+    g = golden["config0"]
+    q, k, v = synth.config0_inputs(0)
+    lk, tk, lv, tv = tables(8, 0, per_group=False)
+    layout = PagedLayout.build_hnd(16, 8, 128, 4, 32, 32)
+    bt = torch.from_numpy(g["c0_block_table"]).to(DEV)
+    slots = synth.slots_for(bt, 16, 0, 1024)
+    cache = torch.zeros((256, layout.block_i32), dtype=torch.int32, device=DEV)
+    write_tokens_to_paged_cache(
+        cache, layout, bt, slots, torch.from_numpy(k).to(DEV), torch.from_numpy(v).to(DEV),
+        q_points_k=lk.to(DEV), q_points_v=lv.to(DEV), thresholds_k=tk.to(DEV), thresholds_v=tv.to(DEV),
+        require_fast=True, stat_dtype=torch.float16,
+    )
+    got = cache.cpu().numpy()
+    assert np.array_equal(got[int(g["c0_page0_id"][0])], g["c0_page0"])
+    assert np.array_equal(np.frombuffer(hashlib.sha256(got.tobytes()).digest(), dtype=np.uint8), g["c0_cache_sha256"])
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("tokens,heads,shared", [(8, 2, True), (513, 8, False), (1, 4, False)])
+def test_writer_matches_oracle_random(tokens, heads, shared, kind):
+    rng = np.random.default_rng(2708 + tokens)
+    dt = KIND_TO_DTYPE[kind]
+    bs, pages = 64, 12
+    geo = oracle.PageGeometry(bs, heads, 128)
+    seed_pages = rng.integers(-(2**31), 2**31, (pages, geo.block_i32)).astype(np.int32)
+    k = torch.from_numpy(rng.standard_normal((tokens, heads, 128)).astype(np.float32)).to(dt)
+    v = torch.from_numpy((rng.standard_normal((tokens, heads, 128)) * 3).astype(np.float32)).to(dt)
+    slots = rng.permutation(pages * bs)[:tokens].astype(np.int64)
+    slots[::17] = -1
+    if shared:
+        lk = tk = lv = tv = None
+        thr_k = thr_v = None
+    else:
+        lk, tk, lv, tv = (t.to(DEV) for t in tables(heads, 5))
+        thr_k, thr_v = tk.float().cpu().numpy(), tv.float().cpu().numpy()
+    expect = seed_pages.copy()
+    oracle.write_pages(expect, geo, slots, k.float().numpy(), v.float().numpy(), thresholds_k=thr_k, thresholds_v=thr_v, stat=kind)
+    cache = torch.from_numpy(seed_pages).to(DEV)
+    layout = PagedLayout.build_hnd(bs, heads, 128, 4, 32, 32)
+    # K and V arrive as views into a fused QKV projection (non-contiguous token stride)
+    fused = torch.zeros((tokens, heads * 3, 128), dtype=dt, device=DEV)
+    fused[:, heads : 2 * heads] = k.to(DEV)
+    fused[:, 2 * heads :] = v.to(DEV)
+    write_tokens_to_paged_cache(
+        cache, layout, None, torch.from_numpy(slots).to(DEV), fused[:, heads : 2 * heads], fused[:, 2 * heads :],
+        q_points_k=lk, q_points_v=lv, thresholds_k=tk, thresholds_v=tv, require_fast=True,
+    )
+    assert np.array_equal(cache.cpu().numpy(), expect)
+
+
+def test_unsorted_thresholds_use_the_counting_rule():
+    heads = 1
+    thr = torch.tensor([0.5, 0.1, 0.9, 0.3, 0.7, 0.2, 0.8, 0.4, 0.6, 0.15, 0.25, 0.35, 0.45, 0.55, 0.65], dtype=torch.float16)
+    lv = torch.linspace(0, 1, 16, dtype=torch.float16)
+    rng = np.random.default_rng(1)
+    x = torch.from_numpy(rng.standard_normal((5, heads, 128)).astype(np.float32)).to(torch.float16)
+    geo = oracle.PageGeometry(16, heads)
+    expect = np.zeros((1, geo.block_i32), dtype=np.int32)
+    slots = np.arange(5, dtype=np.int64)
+    oracle.write_pages(expect, geo, slots, x.float().numpy(), x.float().numpy(),
+                       thresholds_k=thr.float().numpy(), thresholds_v=thr.float().numpy())
+    cache = torch.zeros((1, geo.block_i32), dtype=torch.int32, device=DEV)
+    write_tokens_to_paged_cache(cache, PagedLayout.build_hnd(16, heads, 128, 4, 32, 32), None,
+                                torch.from_numpy(slots).to(DEV), x.to(DEV), x.to(DEV),
+                                q_points_k=lv.to(DEV), q_points_v=lv.to(DEV), thresholds_k=thr.to(DEV), thresholds_v=thr.to(DEV))
+    assert np.array_equal(cache.cpu().numpy(), expect)
+
+
+def test_empty_and_rejected_inputs():
+    layout = PagedLayout.build_hnd(16, 2, 128, 4, 32, 32)
+    cache = torch.zeros((2, layout.block_i32), dtype=torch.int32, device=DEV)
+    empty = torch.zeros((0, 2, 128), dtype=torch.float16, device=DEV)
+    write_tokens_to_paged_cache(cache, layout, None, torch.zeros((0,), dtype=torch.int32, device=DEV), empty, empty, require_fast=True)
+    assert not cache.any()
+    k = torch.zeros((1, 2, 128), dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="fused sm_100a writer"):
+        write_tokens_to_paged_cache(cache.cpu(), layout, None, torch.zeros((1,), dtype=torch.int32), k, k, require_fast=True)
+    with pytest.raises(RuntimeError, match="fused sm_100a writer"):  # no silent fallback without require_fast either
+        write_tokens_to_paged_cache(cache.cpu(), layout, None, torch.zeros((1,), dtype=torch.int32), k, k)
+    bad = PagedLayout.build_hnd(16, 2, 96, 4, 32, 32)
+    with pytest.raises(RuntimeError):
+        write_tokens_to_paged_cache(torch.zeros((2, bad.block_i32), dtype=torch.int32, device=DEV), bad, None,
+                                    torch.zeros((1,), dtype=torch.int32, device=DEV),
+                                    torch.zeros((1, 2, 96), dtype=torch.float16, device=DEV),
+                                    torch.zeros((1, 2, 96), dtype=torch.float16, device=DEV), require_fast=True)

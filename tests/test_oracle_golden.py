@@ -1,0 +1,169 @@
+"""The numpy oracle against vectors produced by the reference's own code
+(tests/golden/make_golden.py) and against the known-answer tests of the
+reference's test-suite (quant/tests/test_paged.py:671-805)."""
+
+import hashlib
+
+import numpy as np
+import pytest
+
+import oracle
+from oracle.paged import ABI_TOKEN_MAJOR, ABI_WORD_MAJOR
+from beyond_kv_cache_b200.synth import config0_inputs
+
+
+def _round_input(x32, kind):
+    return oracle.stat_to_f32(oracle.round_to_stat(x32, kind), kind)
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_exact_threshold_ties(golden, kind):
+    g = golden["kat"]
+    x = g[f"ties_{kind}_x"].reshape(1, 1, 128)
+    enc = oracle.encode_groups(x, g["ties_thresholds"], stat=kind)
+    assert np.array_equal(enc["codes"].reshape(4, 32), g[f"ties_{kind}_codes"])
+    assert np.array_equal(enc["scale_bits"].reshape(4), g[f"ties_{kind}_scale_bits"])
+    assert np.array_equal(enc["mn_bits"].reshape(4), g[f"ties_{kind}_mn_bits"])
+    if kind == "f16":  # every threshold value lands in the bucket to its right
+        assert list(enc["codes"].reshape(4, 32)[0, 2:17]) == list(range(1, 16))
+
+
+def test_division_rounding_boundary(golden):
+    g = golden["kat"]
+    enc = oracle.encode_groups(g["divrn_x"].reshape(1, 1, 128), g["divrn_thresholds"], stat="f16")
+    assert np.array_equal(enc["codes"].reshape(4, 32), g["divrn_codes"])
+    assert np.array_equal(enc["words"].reshape(4, 4), g["divrn_words"])
+    assert np.array_equal(enc["scale_bits"].reshape(4), g["divrn_scale_bits"])
+    assert np.array_equal(enc["mn_bits"].reshape(4), g["divrn_mn_bits"])
+    # the documented known answer: code 11, not 12; scale 19760, minimum -18080
+    assert int(enc["codes"].reshape(4, 32)[0, 2]) == 11
+    assert float(oracle.stat_to_f32(enc["scale_bits"], "f16").reshape(-1)[0]) == 19760.0
+    assert float(oracle.stat_to_f32(enc["mn_bits"], "f16").reshape(-1)[0]) == -18080.0
+
+
+def test_default_tables(golden):
+    g = golden["kat"]
+    assert np.array_equal(oracle.uniform_levels(), g["uniform_levels_f32"])
+    assert np.array_equal(oracle.uniform_thresholds(oracle.uniform_levels()), g["uniform_thresholds_f32"])
+    from oracle.quantizer import default_tables
+
+    lv, th = default_tables()
+    assert np.array_equal(oracle.round_to_stat(lv, "f16"), g["default_levels_bits"])
+    assert np.array_equal(oracle.round_to_stat(th, "f16"), g["default_thresholds_bits"])
+
+
+def test_pack_layout_facts():
+    full = np.full((3, 32), 15, dtype=np.uint8)
+    words = oracle.pack_nibbles(full)
+    assert words.shape == (3, 4) and all(bin(int(w)).count("1") == 32 for w in words.ravel())
+    assert not oracle.pack_nibbles(np.zeros((1, 32), dtype=np.uint8)).any()
+    rng = np.random.default_rng(0)
+    codes = rng.integers(0, 16, (5, 7, 32)).astype(np.uint8)
+    assert np.array_equal(oracle.unpack_nibbles(oracle.pack_nibbles(codes)), codes)
+    # byte j of the little-endian word stream is code[2j] | code[2j+1] << 4
+    b = oracle.pack_nibbles(codes).astype("<u4").view(np.uint8).reshape(5, 7, 16)
+    assert np.array_equal(b, codes[..., 0::2] | (codes[..., 1::2] << 4))
+    with pytest.raises(TypeError):
+        oracle.pack_nibbles(codes.astype(np.int32))
+
+
+def test_page_geometry_matches_reference_layout(golden):
+    for row in golden["kat"]["layout_rows"]:
+        bs, h, d, k_code, k_scale, k_min, v_code, v_scale, v_min, halves, i32 = (int(x) for x in row)
+        geo = oracle.PageGeometry(bs, h, d)
+        assert geo.k_code_off * 2 == k_code
+        assert geo.k_stat_off * 2 == k_scale
+        assert geo.v_code_off * 2 == v_code
+        assert geo.v_stat_off * 2 == v_scale
+        assert geo.block_i32 == i32 and halves == 2 * i32
+    assert oracle.PageGeometry(128, 8).block_i32 == 8 * 5120
+    assert oracle.PageGeometry(16, 8).block_i32 == 5120
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("abi", ["v2", "v1"])
+@pytest.mark.parametrize("bs", [16, 64])
+def test_writer_page_bytes(golden, bs, abi, kind):
+    g = golden["writer"]
+    geo = oracle.PageGeometry(bs, 2, 128, ABI_TOKEN_MAJOR if abi == "v2" else ABI_WORD_MAJOR)
+    pages = 6 if bs == 16 else 2
+    cache = np.random.default_rng(99).integers(-(2**31), 2**31, (pages, geo.block_i32)).astype(np.int32)
+    k = _round_input(g["w_k32"], kind)
+    v = _round_input(g["w_v32"], kind)
+    ek, ev = oracle.write_pages(
+        cache, geo, g[f"w_slots_bs{bs}"], k, v, thresholds_k=g["w_th_k"], thresholds_v=g["w_th_v"], stat=kind
+    )
+    tag = f"bs{bs}_{abi}_{kind}"
+    assert np.array_equal(cache, g[f"w_cache_{tag}"])
+    k_dq = oracle.decode_groups(ek["codes"], g["w_lv_k"], ek["scale_bits"], ek["mn_bits"], stat=kind)
+    v_dq = oracle.decode_groups(ev["codes"], g["w_lv_v"], ev["scale_bits"], ev["mn_bits"], stat=kind)
+    assert np.array_equal(oracle.round_to_stat(k_dq, kind), g[f"w_kdq_bits_{tag}"])
+    assert np.array_equal(oracle.round_to_stat(v_dq, kind), g[f"w_vdq_bits_{tag}"])
+
+
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+def test_readback(golden, kind):
+    g = golden["writer"]
+    geo = oracle.PageGeometry(16, 2, 128)
+    cache = g[f"w_cache_bs16_v2_{kind}"]
+    k, v = oracle.read_request(cache, geo, [2, 0], 20, levels_k=g["w_lv_k"], levels_v=g["w_lv_v"], stat=kind, out=kind)
+    for mine, key in ((k, "k"), (v, "v")):
+        want_bits = g[f"w_read_{key}_bits_bs16_v2_{kind}"].reshape(20, 2, 128)
+        want = oracle.stat_to_f32(want_bits, kind)
+        ok = np.isfinite(want)  # unwritten slots hold random page bytes (possibly NaN statistics)
+        assert ok.mean() > 0.5
+        assert np.array_equal(oracle.round_to_stat(mine, kind)[ok], want_bits[ok])
+        assert not np.isfinite(mine[~ok]).any()
+
+
+def test_config0_encode_and_attention(golden):
+    from beyond_kv_cache_b200 import synth
+
+    g = golden["config0"]
+    q, k, v = config0_inputs(0)
+    digest = hashlib.sha256(np.concatenate([q.ravel(), k.ravel(), v.ravel()]).tobytes()).digest()
+    assert np.array_equal(np.frombuffer(digest, dtype=np.uint8), g["c0_inputs_sha256"]), "input generator drifted"
+    lv_k, th_k = (t.float().numpy() for t in synth.make_tables(8, seed=0, which="k"))
+    lv_v, th_v = (t.float().numpy() for t in synth.make_tables(8, seed=0, which="v"))
+    geo = oracle.PageGeometry(16, 8, 128)
+    bt = g["c0_block_table"]
+    slots = (bt.astype(np.int64)[:, np.arange(1024) // 16] * 16 + np.arange(1024) % 16).reshape(-1)
+    cache = np.zeros((4 * 64, geo.block_i32), dtype=np.int32)
+    ek, _ = oracle.write_pages(cache, geo, slots, k, v, thresholds_k=th_k, thresholds_v=th_v, stat="f16")
+    assert np.array_equal(ek["codes"][:64], g["c0_k_codes_head"])
+    assert np.array_equal(ek["scale_bits"][:64], g["c0_k_scale_bits_head"])
+    assert np.array_equal(ek["mn_bits"][:64], g["c0_k_mn_bits_head"])
+    assert np.array_equal(cache[int(g["c0_page0_id"][0])], g["c0_page0"])
+    assert np.array_equal(
+        np.frombuffer(hashlib.sha256(cache.tobytes()).digest(), dtype=np.uint8), g["c0_cache_sha256"]
+    )
+    out = oracle.decode_attention(
+        q, cache, geo, bt, [1024] * 4, levels_k=lv_k, levels_v=lv_v, softmax_scale=1.0 / np.sqrt(128.0), stat="f16"
+    )
+    # reference SDPA is float32; the oracle sums in float64
+    assert np.abs(out - g["c0_out"]).max() < 2e-5
+    # the unrounded-statistics fake-QDQ path gives the same codes
+    assert np.array_equal(oracle.encode_groups(k[:64], th_k, stat="bf16")["codes"], g["c0_k_codes_head"])
+
+
+def test_merge_partials_equals_full_attention(golden):
+    from beyond_kv_cache_b200 import synth
+
+    rng = np.random.default_rng(5)
+    geo = oracle.PageGeometry(16, 2, 128)
+    T = 100
+    k = rng.standard_normal((T, 2, 128)).astype(np.float32)
+    v = rng.standard_normal((T, 2, 128)).astype(np.float32)
+    q = rng.standard_normal((1, 8, 128)).astype(np.float32)
+    lv, th = (t.float().numpy() for t in synth.make_tables(2, seed=3))
+    cache = np.zeros((7, geo.block_i32), dtype=np.int32)
+    bt = np.array([[3, 1, 4, 6, 0, 2, 5]], dtype=np.int32)
+    slots = bt[0].astype(np.int64)[np.arange(T) // 16] * 16 + np.arange(T) % 16
+    oracle.write_pages(cache, geo, slots, k, v, thresholds_k=th, thresholds_v=th)
+    kw = dict(levels_k=lv, levels_v=lv, softmax_scale=0.088)
+    full = oracle.decode_attention(q, cache, geo, bt, [T], **kw)
+    parts = [oracle.decode_attention(q, cache, geo, bt, [T], kv_range=r, return_partials=True, **kw)
+             for r in [(0, 32), (32, 64), (64, 96), (96, 128), (128, 160)]]
+    merged = oracle.merge_partials(*[np.stack(x) for x in zip(*parts)])
+    assert np.abs(merged - full).max() < 1e-6
+    assert not oracle.decode_attention(q, cache, geo, bt, [0], **kw).any()
