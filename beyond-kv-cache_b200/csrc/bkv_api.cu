@@ -112,6 +112,12 @@ extern "C" int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dty
   return BKV_OK;
 }
 
+extern "C" int bkv_decode_device_status(int* status_out) {
+  if (!status_out) return BKV_ERR_ARG;
+  *status_out = bkv::read_decode_status();
+  return bkv::check_launch("bkv_decode_device_status");
+}
+
 extern "C" int bkv_combine_sm100(const float* o_partial, const float* m_partial,
                                  const float* l_partial, int num_splits, int64_t rows, void* out,
                                  int out_dtype, float* out_f32, bkv_stream_t stream) {
@@ -143,7 +149,7 @@ extern "C" int bkv_decode_range_sm100(const void* q, int64_t q_batch_stride, int
   if (batch == 0) return BKV_OK;
   if (!o_partial || !m_partial || !l_partial) return BKV_ERR_ARG;
   if (token_lo < 0 || token_hi < token_lo) return BKV_ERR_ARG;
-  if (token_lo % block_size) return BKV_ERR_ALIGN;  // ranges start on a page boundary
+  if (token_lo % block_size) return BKV_ERR_ARG;  // ranges start on a page boundary
   p.o_partial = o_partial; p.m_partial = m_partial; p.l_partial = l_partial;
   p.num_splits = 1; p.force_partial = 1;
   p.token_lo = token_lo; p.token_hi = token_hi;

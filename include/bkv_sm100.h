@@ -111,6 +111,14 @@ int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const v
                      bkv_stream_t stream);
 
 /*
+ * Diagnostic: reads and clears the device-side status word of the decode kernels
+ * (0 = fine; 1 / 2 = a bounded wait inside the tensor-core kernel gave up after 2 s
+ * instead of spinning forever).  Synchronises the device.  No counterpart in the
+ * reference.
+ */
+int bkv_decode_device_status(int* status_out);
+
+/*
  * Log-sum-exp merge of split partials.  Replaces reduction_parallel_weights /
  * reduction_cta4_weights / reduction_warp_parallel_weights
  * (quant/fa4_cute/beyond_mixed_decode_sm100.py:2935-3214).  m_partial is in the

@@ -178,3 +178,13 @@ def test_launcher_rejects_bad_contracts():
         rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=bt,
                                  seq_lens=torch.ones(1, dtype=torch.int32, device=DEV), k_qpoints_lane_major=rk,
                                  v_qpoints_code_major=rv, out=torch.empty_like(q), workspace={}, softmax_scale=0.1)
+
+
+def test_zz_no_bounded_wait_gave_up():
+    """Runs after the decode cases of this file: the tensor-core kernel's bounded waits
+    (producer / consumer mbarrier polls) must never have expired."""
+    import ctypes
+
+    status = ctypes.c_int(-1)
+    _lib.call("bkv_decode_device_status", ctypes.byref(status))
+    assert status.value == 0
