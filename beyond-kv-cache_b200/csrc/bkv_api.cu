@@ -3,6 +3,7 @@
 
 #include <climits>
 #include <cstdio>
+#include <cstdlib>
 
 #include "bkv_decode_common.cuh"
 
@@ -20,6 +21,22 @@ int check_launch(const char* where) {
   if (e == cudaSuccess) return BKV_OK;
   set_last_cuda_error(e, where);
   return BKV_ERR_CUDA;
+}
+
+// Tuning / experiment knobs read once from the environment: BKV_MMA_CONFIG selects the
+// (warps, ring depth) instantiation of the tensor-core kernel, BKV_DEBUG_FLAGS is OR-ed
+// into the flags of every decode call.
+static int env_int(const char* name) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : 0;
+}
+static int mma_config() {
+  static const int c = env_int("BKV_MMA_CONFIG");
+  return c;
+}
+static int debug_flags() {
+  static const int f = env_int("BKV_DEBUG_FLAGS");
+  return f;
 }
 
 static int fill_decode_params(DecodeParams& p, const void* q, int64_t q_batch_stride, int q_dtype,
@@ -53,7 +70,7 @@ static int fill_decode_params(DecodeParams& p, const void* q, int64_t q_batch_st
   p.o_partial = nullptr; p.m_partial = nullptr; p.l_partial = nullptr;
   p.num_splits = 1; p.token_lo = 0; p.token_hi = INT_MAX; p.force_partial = 0;
   p.scale_log2 = softmax_scale * kLog2e;
-  p.flags = flags;
+  p.flags = flags | debug_flags();
   return BKV_OK;
 }
 
@@ -103,8 +120,8 @@ extern "C" int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dty
   p.token_hi = max_seq_len;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int launched = BKV_ERR_UNSUPPORTED;
-  if (variant == 0 || variant == 2) launched = launch_decode_mma(p, s);
-  if (launched == BKV_ERR_UNSUPPORTED && variant != 2) launched = launch_decode_scalar(p, s);
+  if (variant != 1) launched = launch_decode_mma(p, s, variant >= 20 ? variant - 20 : mma_config());
+  if (launched == BKV_ERR_UNSUPPORTED && variant <= 1) launched = launch_decode_scalar(p, s);
   if (launched != BKV_OK) return launched;
   if (num_splits > 1)
     return launch_combine(o_partial, m_partial, l_partial, num_splits,
@@ -154,7 +171,7 @@ extern "C" int bkv_decode_range_sm100(const void* q, int64_t q_batch_stride, int
   p.num_splits = 1; p.force_partial = 1;
   p.token_lo = token_lo; p.token_hi = token_hi;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int launched = launch_decode_mma(p, s);
+  int launched = launch_decode_mma(p, s, mma_config());
   if (launched == BKV_ERR_UNSUPPORTED) launched = launch_decode_scalar(p, s);
   return launched;
 }

@@ -1,10 +1,11 @@
 // Tensor-core fused paged split-KV decode attention over the packed 4-bit cache (sm_100a).
 //
-// One CTA serves one (split, kv-head [, query-head quad], request).  NW consumer warps
-// each own a private ring of 16-token tiles that a producer warp fills with 1-D bulk
-// copies (cp.async.bulk + mbarrier); a warp keeps its own online-softmax state, so
-// there is no cross-warp synchronisation inside the main loop.  Warp partials are
-// merged through shared memory at the end, split partials by the combine kernel.
+// One CTA serves one (split, kv-head [, query-head quad], request).  Each of its NW warps
+// owns a private ring of 16-token tiles which it fills itself with 1-D bulk copies
+// (cp.async.bulk + mbarrier, five lanes issue the five chunks of a tile in parallel) and
+// keeps its own online-softmax state, so there is no cross-warp synchronisation inside
+// the main loop.  Warp partials are merged through shared memory at the end, split
+// partials by the combine kernel.
 //
 // Dequantisation never materialises K or V.  A 256-entry table indexed by a whole
 // code BYTE returns the two fp16 levels of its two nibbles as one MMA operand
@@ -18,25 +19,41 @@
 //   QK : S^T[(h,g), token] = Q_blockdiag[(h,g), d] * Lk[d, token]   (k-slots of lane tig belong to group tig)
 //   PV : O[d, (h,g')]      = Lv^T[d, token] * (p*scale_v)[token, (h,g')]   (rows of lane gid belong to group gid/2)
 // Products whose row group and column group differ are computed and discarded.
+//
+// The table sits at the fixed shared-memory address 0x10000, so a look-up address is a
+// single byte-permute of (code word, lane constant) with no addition.  Tokens of a tile
+// are assigned to MMA columns / k-slots through a fixed permutation (kTok0 / kTok1) that
+// makes every 128-bit code load of a quarter-warp hit eight distinct bank groups.
 #include <math_constants.h>
 
 #include "bkv_decode_common.cuh"
 
 namespace bkv {
 
-__device__ int g_decode_status = 0;  // non-zero: a bounded wait gave up (1 producer, 2 consumer)
+__device__ int g_decode_status = 0;  // non-zero: 1/2 a bounded wait gave up, 3 unexpected smem base
 
 namespace {
 
 constexpr int kTile = 16;
-constexpr int kTileBytes = 2560;
+constexpr int kTileBytes = 2592;
 constexpr int kOffKCode = 0;
 constexpr int kOffKStat = 1024;
-constexpr int kOffVCode = 1280;
-constexpr int kOffVStat = 2304;
-constexpr int kLutBytes = 65536;
+constexpr int kOffVCode = 1280;   // tokens 0-7; tokens 8-15 start 32 bytes later than contiguous
+constexpr int kVCodeSkew = 32;
+constexpr int kOffVStat = 2336;
+constexpr uint32_t kSmemBase = 0x400;   // dynamic shared memory starts after the 1 KB the system reserves
+constexpr uint32_t kLutAddr = 0x10000;  // 64 KB table, 64 KB aligned: address = 0x10000 | byte << 8 | slot
+constexpr uint32_t kRingHi = 0x20000;
+constexpr int kCtrlBytes = 2048;        // barriers, tile lengths, fp16 level tables
+constexpr uint32_t kRingLo = kSmemBase + kCtrlBytes;
+constexpr int kLoSlots = (kLutAddr - kRingLo) / kTileBytes;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait that lasts 2 s gives up
-constexpr float kRescaleThreshold = 8.f;  // log2 units: p stays below 2^8
+constexpr float kRescaleThreshold = 8.f;                     // log2 units: p stays below 2^8
+// token held by MMA column / k-slot n of the first (kTok0) and second (kTok1) half of a tile
+constexpr uint32_t kTok0 = 0xEFDC2310u;  // 0,1,3,2,12,13,15,14
+constexpr uint32_t kTok1 = 0x6754AB98u;  // 8,9,11,10,4,5,7,6
+
+constexpr int BKV_FLAG_DEBUG_NOLOAD = 0x100;  // timing experiment: reuse the first ring fill
 
 // ---- PTX helpers --------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -71,8 +88,8 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait bookkeeping: returns true once `limit` nanoseconds have passed since the
-// first failed poll (the clock is only read every 256 polls).
+// Bounded wait bookkeeping: true once kWaitLimitNs have passed since the first failed
+// poll (the clock is only read every 256 polls).
 struct WaitBudget {
   uint32_t polls = 0;
   unsigned long long start = 0;
@@ -107,39 +124,84 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+__device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: 2 ulp, exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void mma16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {  // c = a*b (no accumulator input)
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
-__device__ __forceinline__ float lo16_to_f32(uint32_t w, bool bf16) {
-  return bf16 ? __uint_as_float(w << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xFFFFu)));
+// Table look-up: the address is complete, no base is added.  Not volatile: the table is
+// constant once built, so the compiler may schedule these freely.
+__device__ __forceinline__ uint32_t lut_load(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
 }
-__device__ __forceinline__ float hi16_to_f32(uint32_t w, bool bf16) {
-  return bf16 ? __uint_as_float(w & 0xFFFF0000u) : __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
+// Ring loads are volatile: they stay, in program order, between the full-barrier wait of
+// their tile and the bulk copies that later refill the same ring stage.
+__device__ __forceinline__ uint4 ring_load128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint2 ring_load64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(IMM));
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+template <bool BF16>
+__device__ __forceinline__ float2 stat_word_to_f32(uint32_t w) {  // (scale, minimum)
+  if (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+__device__ __forceinline__ uint32_t slot_addr(int slot) {
+  return slot < kLoSlots ? kRingLo + slot * kTileBytes : kRingHi + (slot - kLoSlots) * kTileBytes;
 }
 
 template <int NW, int STAGES>
-struct SmemLayout {
-  static constexpr int kRing = kLutBytes;
-  static constexpr int kRingBytes = NW * STAGES * kTileBytes;
-  static constexpr int kFullBar = kRing + kRingBytes;
-  static constexpr int kEmptyBar = kFullBar + NW * STAGES * 8;
-  static constexpr int kNValid = kEmptyBar + NW * STAGES * 8;
-  static constexpr int kLevels = kNValid + NW * STAGES * 4;  // fp16 [K|V][4][16]
-  static constexpr int kTotal = kLevels + 2 * 4 * 16 * 2;
-  // epilogue overlay on the ring: O partials [NW][4][128] f32, then m, l [NW][4]
-  static constexpr int kMergeO = kRing;
-  static constexpr int kMergeM = kMergeO + NW * 4 * kHeadDim * 4;
-  static constexpr int kMergeL = kMergeM + NW * 4 * 4;
-  static_assert(kMergeL + NW * 4 * 4 <= kFullBar, "merge overlay must fit in the ring");
+struct Smem {
+  static constexpr int kSlots = NW * STAGES;
+  static_assert(kSlots <= 64, "control block holds at most 64 ring slots");
+  static constexpr uint32_t kFullBar = kSmemBase;        // 8 B each
+  static constexpr uint32_t kLevels = kSmemBase + 1280;  // fp16 [K|V][4][16]
+  static constexpr int kMergeBytes = NW * 4 * kHeadDim * 4 + NW * 4 * 4 * 2;
+  static constexpr int kHiSlots = kSlots > kLoSlots ? kSlots - kLoSlots : 0;
+  static constexpr int kHiBytes = kHiSlots * kTileBytes > kMergeBytes ? kHiSlots * kTileBytes : kMergeBytes;
+  static constexpr int kDynBytes = static_cast<int>(kRingHi - kSmemBase) + kHiBytes;
+  static_assert(kDynBytes <= 232448, "exceeds the 227 KB a CTA can opt into");
+  // epilogue overlay in the high region (all ring traffic has drained by then)
+  static constexpr uint32_t kMergeO = kRingHi;
+  static constexpr uint32_t kMergeM = kMergeO + NW * 4 * kHeadDim * 4;
+  static constexpr uint32_t kMergeL = kMergeM + NW * 4 * 4;
 };
 
+// registers a thread may use when one CTA of NW warps owns the SM (64 K registers, allocated in eights)
+constexpr int max_regs_for(int nw) { return (65536 / (nw * 32)) / 8 * 8 > 255 ? 255 : (65536 / (nw * 32)) / 8 * 8; }
+
 template <int NW, int STAGES, bool STAT_BF16>
-__global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const DecodeParams p, const int quads) {
-  using L = SmemLayout<NW, STAGES>;
+__global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodeParams p, const int quads) {
+  using L = Smem<NW, STAGES>;
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t smem_base = smem_u32(smem);
+  if (smem_base != kSmemBase) {  // the fixed-address table needs the documented layout
+    if (threadIdx.x == 0) atomicExch(&g_decode_status, 3);
+    return;
+  }
+  auto gptr = [&](uint32_t shared_addr) { return smem + (shared_addr - kSmemBase); };
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3;
 
@@ -151,7 +213,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
   const int nh = min(4, gqa - quad * 4);
   const int S = p.num_splits;
   const int BS = p.block_size;
-  const int tiles_per_page = BS / kTile;
+  const int log2r = 31 - __clz(BS / kTile);  // tiles per page is a power of two
+  const int tiles_per_page = 1 << log2r;
+  const bool noload = (p.flags & BKV_FLAG_DEBUG_NOLOAD) != 0;
 
   if (p.flags & BKV_FLAG_PDL_WAIT) pdl_wait();
 
@@ -174,127 +238,89 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
       }
     }
   }
+  const int my_tiles = n_tiles > warp ? (n_tiles - warp + NW - 1) / NW : 0;  // tiles warp, warp+NW, ...
 
   if (tid == 0) {
-    for (int i = 0; i < NW * STAGES; ++i) {
-      mbar_init(smem_base + L::kFullBar + 8 * i, 1);
-      mbar_init(smem_base + L::kEmptyBar + 8 * i, 1);
-    }
+    for (int i = 0; i < L::kSlots; ++i) mbar_init(L::kFullBar + 8 * i, 1);
     fence_barrier_init();
   }
   __syncthreads();
 
-  // =====================================================================================
-  // Producer warp: lane w feeds consumer warp w.  The lanes run in lock step; a lane whose
-  // next ring slot is still in use simply sits the round out.
-  // =====================================================================================
-  if (warp == NW) {
-    const int w = lane;
-    const int my_tiles = (w < NW && n_tiles > w) ? (n_tiles - w + NW - 1) / NW : 0;
-    const PageGeom g = make_geom(BS, p.heads_kv);
-    const int32_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
-    const char* cache_bytes = reinterpret_cast<const char*>(p.cache);
-    constexpr int PF = 4;
-    int32_t phys_next[PF];
-    auto page_of = [&](int k) {
-      const int j = w + k * NW;
-      return page_lo + split + S * (j / tiles_per_page);
-    };
-#pragma unroll
-    for (int i = 0; i < PF; ++i) phys_next[i] = i < my_tiles ? bt_row[page_of(i)] : 0;
-    int32_t phys_cur[PF] = {0, 0, 0, 0};
-    int k = 0;
-    WaitBudget idle;
-    while (true) {
-      const bool active = k < my_tiles;
-      if (!__any_sync(0xffffffffu, active)) break;
-      bool can = false;
-      if (active) {
-        const int use = k / STAGES;
-        const int stage = k - use * STAGES;
-        can = use == 0 || mbar_try_wait(smem_base + L::kEmptyBar + 8 * (w * STAGES + stage), (use - 1) & 1);
-      }
-      if (can) {
-        if ((k & (PF - 1)) == 0) {
-#pragma unroll
-          for (int i = 0; i < PF; ++i) {
-            phys_cur[i] = phys_next[i];
-            phys_next[i] = (k + PF + i) < my_tiles ? bt_row[page_of(k + PF + i)] : 0;
-          }
-        }
-        int64_t phys = phys_cur[0];
-#pragma unroll
-        for (int i = 1; i < PF; ++i)
-          if ((k & (PF - 1)) == i) phys = phys_cur[i];
-        const int stage = k % STAGES;
-        const int slot = w * STAGES + stage;
-        const int j = w + k * NW;
-        const int sub = j % tiles_per_page;
-        const int tok0 = page_of(k) * BS + sub * kTile;
-        const uint32_t full = smem_base + L::kFullBar + 8 * slot;
-        int* nvalid = reinterpret_cast<int*>(smem + L::kNValid) + slot;
-        if (phys < 0 || phys >= p.num_pages) {
-          *nvalid = 0;  // unmapped page: the consumer skips the tile
-          mbar_arrive(full);
-        } else {
-          *nvalid = min(kTile, hi - tok0);
-          const uint32_t dst = smem_base + L::kRing + slot * kTileBytes;
-          const char* pg = cache_bytes + phys * p.page_stride * 4;
-          mbar_arrive_expect_tx(full, kTileBytes);
-          const int code_off = head * (BS * kWordsPerHead) + sub * (kTile * kWordsPerHead);
-          bulk_copy_g2s(dst + kOffKCode, pg + 4 * (g.k_code_off + code_off), 1024, full);
-          bulk_copy_g2s(dst + kOffKStat, pg + 4 * (g.k_stat_off + head * (BS * 4) + sub * (kTile * 4)), 256, full);
-          bulk_copy_g2s(dst + kOffVCode, pg + 4 * (g.v_code_off + code_off), 1024, full);
-          const char* vs = pg + 4 * (g.v_stat_off + head * (4 * BS) + sub * kTile);
-          if (tiles_per_page == 1) {
-            bulk_copy_g2s(dst + kOffVStat, vs, 256, full);
-          } else {
-#pragma unroll
-            for (int gg = 0; gg < 4; ++gg) bulk_copy_g2s(dst + kOffVStat + gg * 64, vs + 4 * gg * BS, 64, full);
-          }
-        }
-        ++k;
-      }
-      if (!__any_sync(0xffffffffu, can)) {
-        if (__any_sync(0xffffffffu, idle.expired())) {
-          atomicExch(&g_decode_status, 1);
-          break;
-        }
-        __nanosleep(40);
-      } else {
-        idle.reset();
-      }
+  // ---- this warp's loader: lane c issues chunk c of a tile --------------------------------
+  // chunks: 0 K codes (1024 B), 1 K statistics (256), 2/3 V codes of tokens 0-7 / 8-15 (512 each),
+  // then V statistics: one 256 B chunk for 16-token pages, else one 64 B chunk per group.
+  const PageGeom geo = make_geom(BS, p.heads_kv);
+  const int n_chunks = tiles_per_page == 1 ? 5 : 8;
+  uint32_t ch_src = 0, ch_sub = 0, ch_dst = 0, ch_bytes = 0;
+  {
+    const uint32_t code_head = head * (BS * kWordsPerHead) * 4;
+    if (lane == 0) { ch_src = geo.k_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffKCode; ch_bytes = 1024; }
+    if (lane == 1) { ch_src = (geo.k_stat_off + head * (BS * 4)) * 4; ch_sub = 256; ch_dst = kOffKStat; ch_bytes = 256; }
+    if (lane == 2) { ch_src = geo.v_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffVCode; ch_bytes = 512; }
+    if (lane == 3) { ch_src = geo.v_code_off * 4 + code_head + 512; ch_sub = 1024; ch_dst = kOffVCode + 512 + kVCodeSkew; ch_bytes = 512; }
+    if (lane >= 4 && lane < n_chunks) {
+      const int gg = lane - 4;
+      ch_src = (geo.v_stat_off + head * (4 * BS) + gg * BS) * 4;
+      ch_sub = 64;
+      ch_dst = kOffVStat + gg * 64;
+      ch_bytes = tiles_per_page == 1 ? 256 : 64;
     }
-    return;
+  }
+  const int32_t* bt_row = p.block_table + static_cast<int64_t>(b) * p.bt_stride;
+  const char* src_base = reinterpret_cast<const char*>(p.cache) + ch_src;  // this lane's chunk inside page 0
+  const int64_t page_bytes = p.page_stride * 4;
+  const uint32_t num_pages_u = static_cast<uint32_t>(min(p.num_pages, static_cast<int64_t>(0x7fffffff)));
+  auto page_of = [&](int ki) { return page_lo + split + S * ((warp + ki * NW) >> log2r); };
+  // lane l holds the physical page of tile (base + l); the next 32 are fetched one batch ahead
+  int32_t phys_cur = lane < my_tiles ? bt_row[page_of(lane)] : 0;
+  int32_t phys_nxt = 32 + lane < my_tiles ? bt_row[page_of(32 + lane)] : 0;
+  uint32_t bad_slots = 0;  // bit s: the tile now in ring stage s maps to no page
+  auto issue_tile = [&](int ki) {
+    if (ki != 0 && (ki & 31) == 0) {
+      phys_cur = phys_nxt;
+      phys_nxt = ki + 32 + lane < my_tiles ? bt_row[page_of(ki + 32 + lane)] : 0;
+    }
+    uint32_t phys = static_cast<uint32_t>(__shfl_sync(0xffffffffu, phys_cur, ki & 31));
+    const int stage = ki % STAGES;
+    const int slot = warp * STAGES + stage;
+    const bool bad = phys >= num_pages_u;  // also catches negative ids
+    bad_slots = bad ? (bad_slots | (1u << stage)) : (bad_slots & ~(1u << stage));
+    if (bad) phys = 0;
+    const uint32_t sub = (warp + ki * NW) & (tiles_per_page - 1);
+    const uint32_t full = L::kFullBar + 8 * slot;
+    if (lane == 0) mbar_arrive_expect_tx(full, 2560);
+    __syncwarp();
+    if (lane < n_chunks)
+      bulk_copy_g2s(slot_addr(slot) + ch_dst, src_base + phys * page_bytes + sub * ch_sub, ch_bytes, full);
+  };
+  {
+    const int first = noload ? min(my_tiles, STAGES) : min(my_tiles, STAGES);
+    for (int ki = 0; ki < first; ++ki) issue_tile(ki);
   }
 
-  // =====================================================================================
-  // Consumer warps
-  // =====================================================================================
-  const int cthreads = NW * 32;
   {  // level tables -> fp16 in shared memory
-    __half* lv = reinterpret_cast<__half*>(smem + L::kLevels);
-    for (int i = tid; i < 128; i += cthreads) {
+    __half* lv = reinterpret_cast<__half*>(gptr(L::kLevels));
+    for (int i = tid; i < 128; i += NW * 32) {
       const int which = i >> 6, g = (i >> 4) & 3, c = i & 15;
       lv[i] = __float2half_rn(which ? load_v_level(p, head, g, c) : load_k_level(p, head, g, c));
     }
   }
-  consumer_bar_sync(cthreads);
+  __syncthreads();
   {  // byte -> (level[low nibble], level[high nibble]) table, one copy per bank
-    const unsigned short* lv = reinterpret_cast<const unsigned short*>(smem + L::kLevels);
+    const unsigned short* lv = reinterpret_cast<const unsigned short*>(gptr(L::kLevels));
     const int kg = lane & 3, vg = lane >> 3;
     for (int e = warp; e < 256; e += NW) {
       const uint32_t kval = lv[kg * 16 + (e & 15)] | (static_cast<uint32_t>(lv[kg * 16 + (e >> 4)]) << 16);
       const uint32_t vval = lv[64 + vg * 16 + (e & 15)] | (static_cast<uint32_t>(lv[64 + vg * 16 + (e >> 4)]) << 16);
-      uint32_t* row = reinterpret_cast<uint32_t*>(smem + e * 256);
+      uint32_t* row = reinterpret_cast<uint32_t*>(gptr(kLutAddr + e * 256));
       row[lane] = kval;
       row[32 + lane] = vval;
     }
   }
 
   // ---- query fragments (A operand of QK), pre-scaled by softmax_scale * log2(e) --------
-  const int hsel = gid & 3;          // query head of this lane's score / B columns
-  const int grow = 2 * (gid >> 2);   // K group of MMA row gid (row gid+8 is group grow+1)
+  const int hsel = gid & 3;         // query head of this lane's scores / B columns
+  const int grow = 2 * (gid >> 2);  // K group of MMA row gid (row gid+8 is group grow+1)
   uint32_t qa[8][4];
   float qs0, qs1;
   {
@@ -319,11 +345,33 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
     qs0 = __shfl_sync(0xffffffffu, qsum, gid * 4 + grow);
     qs1 = __shfl_sync(0xffffffffu, qsum, gid * 4 + grow + 1);
   }
-  consumer_bar_sync(cthreads);  // table complete
+  __syncthreads();  // table complete
 
+  // ---- per-lane constants ---------------------------------------------------------------
   const int gv = gid >> 1, vu = gid & 1;  // V group / nibble parity of this lane's MMA rows
-  const uint32_t klane = lane * 4, vlane = lane * 4 + 128;
-  const unsigned char* lut = smem;
+  const uint32_t klane = kLutAddr | (lane * 4), vlane = kLutAddr | (lane * 4 + 128);
+  // token whose K codes this lane feeds into column gid of the two QK halves
+  const int kprov0 = (kTok0 >> (4 * gid)) & 15, kprov1 = (kTok1 >> (4 * gid)) & 15;
+  const uint32_t kc_off0 = kOffKCode + kprov0 * 64 + tig * 16, kc_off1 = kOffKCode + kprov1 * 64 + tig * 16;
+  // tokens of this lane's columns / k-slots 2tig, 2tig+1 in the two halves
+  int tk[2][2];
+  tk[0][0] = (kTok0 >> (8 * tig)) & 15;
+  tk[0][1] = (kTok0 >> (8 * tig + 4)) & 15;
+  tk[1][0] = (kTok1 >> (8 * tig)) & 15;
+  tk[1][1] = (kTok1 >> (8 * tig + 4)) & 15;
+  uint32_t ks_off[2][2], vc_off[2][2], vs_off[2];
+#pragma unroll
+  for (int o = 0; o < 2; ++o) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      ks_off[o][e] = kOffKStat + tk[o][e] * 16 + grow * 4;
+      vc_off[o][e] = kOffVCode + tk[o][e] * 64 + (tk[o][e] >= 8 ? kVCodeSkew : 0) + gv * 16;
+    }
+    vs_off[o] = kOffVStat + ((gid >> 2) * kTile + min(tk[o][0], tk[o][1])) * 4;
+  }
+  const bool pair_swapped = tk[0][0] > tk[0][1];  // odd tig: the pair sits in memory as (second, first)
+  const uint32_t sel_scale = pair_swapped ? 0x1054u : 0x5410u, sel_min = pair_swapped ? 0x3276u : 0x7632u;
+  const int sh0 = 4 * vu, sh1 = 4 - 4 * vu;
 
   float oacc[8][2][4];
   float cmin[2][4];
@@ -338,16 +386,15 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
 #pragma unroll
     for (int c = 0; c < 4; ++c) cmin[jn][c] = 0.f;
   float m_used = -CUDART_INF_F, l_run = 0.f;
-  bool gave_up = false;
 
-  int k = 0;
-  for (int j = warp; j < n_tiles && !gave_up; j += NW, ++k) {
+  for (int k = 0; k < my_tiles; ++k) {
     const int use = k / STAGES;
     const int stage = k - use * STAGES;
     const int slot = warp * STAGES + stage;
-    {
-      const uint32_t full = smem_base + L::kFullBar + 8 * slot;
+    if (!(noload && use > 0)) {
+      const uint32_t full = L::kFullBar + 8 * slot;
       WaitBudget budget;
+      bool gave_up = false;
       while (!mbar_try_wait(full, use & 1)) {
         if (__any_sync(0xffffffffu, budget.expired())) {
           gave_up = true;
@@ -359,46 +406,53 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
         break;
       }
     }
-    const int nv = reinterpret_cast<const int*>(smem + L::kNValid)[slot];
-    const unsigned char* st = smem + L::kRing + slot * kTileBytes;
+    const int j = warp + k * NW;
+    const int tok0 = (page_lo + split + S * (j >> log2r)) * BS + (j & (tiles_per_page - 1)) * kTile;
+    const int nv = (bad_slots >> stage) & 1 ? 0 : min(kTile, hi - tok0);
+    const uint32_t sb = slot_addr(slot);
     if (nv > 0) {
       // ------------------------------ S^T = Q * Lk^T -------------------------------------
       float sacc[2][4];
 #pragma unroll
       for (int o = 0; o < 2; ++o) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) sacc[o][c] = 0.f;
-        const uint4 kw = *reinterpret_cast<const uint4*>(st + kOffKCode + (8 * o + gid) * 64 + tig * 16);
+        const uint4 kw = ring_load128(sb + (o ? kc_off1 : kc_off0));
         const uint32_t w4[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
           const uint32_t wd = w4[jj >> 1];
-          const uint32_t off0 = __byte_perm(wd, klane, (jj & 1) ? 0x5524 : 0x5504);
-          const uint32_t off1 = __byte_perm(wd, klane, (jj & 1) ? 0x5534 : 0x5514);
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(lut + off0);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(lut + off1);
-          mma16816(sacc[o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], b0, b1);
+          const uint32_t b0 = lut_load(__byte_perm(wd, klane, (jj & 1) ? 0x7624 : 0x7604));
+          const uint32_t b1 = lut_load(__byte_perm(wd, klane, (jj & 1) ? 0x7634 : 0x7614));
+          if (jj == 0) mma16816_zero(sacc[o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], b0, b1);
+          else mma16816(sacc[o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], b0, b1);
         }
       }
       // ------------------------------ scores of this lane ---------------------------------
       float s[2][2];
 #pragma unroll
       for (int o = 0; o < 2; ++o) {
-        const int t0 = 8 * o + 2 * tig;
-        const uint2 st0 = *reinterpret_cast<const uint2*>(st + kOffKStat + t0 * 16 + grow * 4);
-        const uint2 st1 = *reinterpret_cast<const uint2*>(st + kOffKStat + (t0 + 1) * 16 + grow * 4);
-        float p0 = lo16_to_f32(st0.x, STAT_BF16) * sacc[o][0];
-        p0 = fmaf(hi16_to_f32(st0.x, STAT_BF16), qs0, p0);
-        p0 = fmaf(lo16_to_f32(st0.y, STAT_BF16), sacc[o][2], p0);
-        p0 = fmaf(hi16_to_f32(st0.y, STAT_BF16), qs1, p0);
-        float p1 = lo16_to_f32(st1.x, STAT_BF16) * sacc[o][1];
-        p1 = fmaf(hi16_to_f32(st1.x, STAT_BF16), qs0, p1);
-        p1 = fmaf(lo16_to_f32(st1.y, STAT_BF16), sacc[o][3], p1);
-        p1 = fmaf(hi16_to_f32(st1.y, STAT_BF16), qs1, p1);
+        const uint2 st0 = ring_load64<0>(sb + ks_off[o][0]);
+        const uint2 st1 = ring_load64<0>(sb + ks_off[o][1]);
+        const float2 a0 = stat_word_to_f32<STAT_BF16>(st0.x), b0 = stat_word_to_f32<STAT_BF16>(st0.y);
+        const float2 a1 = stat_word_to_f32<STAT_BF16>(st1.x), b1 = stat_word_to_f32<STAT_BF16>(st1.y);
+        float p0 = a0.x * sacc[o][0];
+        p0 = fmaf(a0.y, qs0, p0);
+        p0 = fmaf(b0.x, sacc[o][2], p0);
+        p0 = fmaf(b0.y, qs1, p0);
+        float p1 = a1.x * sacc[o][1];
+        p1 = fmaf(a1.y, qs0, p1);
+        p1 = fmaf(b1.x, sacc[o][3], p1);
+        p1 = fmaf(b1.y, qs1, p1);
         p0 += __shfl_xor_sync(0xffffffffu, p0, 16);
         p1 += __shfl_xor_sync(0xffffffffu, p1, 16);
-        s[o][0] = (t0 < nv) ? p0 : -CUDART_INF_F;
-        s[o][1] = (t0 + 1 < nv) ? p1 : -CUDART_INF_F;
+        s[o][0] = p0;
+        s[o][1] = p1;
+      }
+      if (nv < kTile) {
+#pragma unroll
+        for (int o = 0; o < 2; ++o)
+#pragma unroll
+          for (int e = 0; e < 2; ++e)
+            if (tk[o][e] >= nv) s[o][e] = -CUDART_INF_F;
       }
       // ------------------------------ online softmax --------------------------------------
       float tmax = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -407,7 +461,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
       const bool need = tmax > m_used + kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
         const float m_new = need ? tmax : m_used;
-        const float corr = (m_new == -CUDART_INF_F) ? 1.f : exp2f(m_used - m_new);
+        const float corr = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_used - m_new);
         m_used = m_new;
         l_run *= corr;
         const float ce = __shfl_sync(0xffffffffu, corr, ((2 * tig) & 3) * 4);
@@ -432,7 +486,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
       uint32_t ph[2];
 #pragma unroll
       for (int o = 0; o < 2; ++o) {
-        const float e0 = exp2f(s[o][0] - m_used), e1 = exp2f(s[o][1] - m_used);
+        const float e0 = fast_exp2(s[o][0] - m_used), e1 = fast_exp2(s[o][1] - m_used);
         l_run += e0 + e1;
         ph[o] = pack_half2(e0, e1);
       }
@@ -440,22 +494,21 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
       uint32_t wb[2][2], mb[2][2];
 #pragma unroll
       for (int jn = 0; jn < 2; ++jn) {
-        const int gp = 2 * jn + (gid >> 2);
 #pragma unroll
         for (int o = 0; o < 2; ++o) {
-          const int t0 = 8 * o + 2 * tig;
-          const uint2 vs = *reinterpret_cast<const uint2*>(st + kOffVStat + (gp * kTile + t0) * 4);
+          const uint2 vs = jn ? ring_load64<2 * kTile * 4>(sb + vs_off[o]) : ring_load64<0>(sb + vs_off[o]);
           uint32_t sc2, mn2;
           if (STAT_BF16) {
-            sc2 = pack_half2(__uint_as_float(vs.x << 16), __uint_as_float(vs.y << 16));
-            mn2 = pack_half2(__uint_as_float(vs.x & 0xFFFF0000u), __uint_as_float(vs.y & 0xFFFF0000u));
+            const uint32_t first = pair_swapped ? vs.y : vs.x, second = pair_swapped ? vs.x : vs.y;
+            sc2 = pack_half2(__uint_as_float(first << 16), __uint_as_float(second << 16));
+            mn2 = pack_half2(__uint_as_float(first & 0xFFFF0000u), __uint_as_float(second & 0xFFFF0000u));
           } else {
-            sc2 = __byte_perm(vs.x, vs.y, 0x5410);
-            mn2 = __byte_perm(vs.x, vs.y, 0x7632);
+            sc2 = __byte_perm(vs.x, vs.y, sel_scale);
+            mn2 = __byte_perm(vs.x, vs.y, sel_min);
           }
           uint32_t wv = hmul2_u32(ph[o], sc2), mv = hmul2_u32(ph[o], mn2);
           if (nv < kTile) {  // stale statistics behind the last token may be NaN/Inf
-            const uint32_t keep = (t0 < nv ? 0x0000FFFFu : 0u) | (t0 + 1 < nv ? 0xFFFF0000u : 0u);
+            const uint32_t keep = (tk[o][0] < nv ? 0x0000FFFFu : 0u) | (tk[o][1] < nv ? 0xFFFF0000u : 0u);
             wv &= keep;
             mv &= keep;
           }
@@ -465,27 +518,25 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
       }
       // ------------------------------ O += Lv^T * W ---------------------------------------
       {
-        const unsigned char* vc = st + kOffVCode + gv * 16;
-        const uint4 x00 = *reinterpret_cast<const uint4*>(vc + (2 * tig) * 64);
-        const uint4 x01 = *reinterpret_cast<const uint4*>(vc + (2 * tig + 1) * 64);
-        const uint4 x10 = *reinterpret_cast<const uint4*>(vc + (8 + 2 * tig) * 64);
-        const uint4 x11 = *reinterpret_cast<const uint4*>(vc + (9 + 2 * tig) * 64);
+        const uint4 x00 = ring_load128(sb + vc_off[0][0]);
+        const uint4 x01 = ring_load128(sb + vc_off[0][1]);
+        const uint4 x10 = ring_load128(sb + vc_off[1][0]);
+        const uint4 x11 = ring_load128(sb + vc_off[1][1]);
         const uint32_t a00[4] = {x00.x, x00.y, x00.z, x00.w}, a01[4] = {x01.x, x01.y, x01.z, x01.w};
         const uint32_t a10[4] = {x10.x, x10.y, x10.z, x10.w}, a11[4] = {x11.x, x11.y, x11.z, x11.w};
-        const int sh0 = 4 * vu, sh1 = 4 - 4 * vu;
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
           const uint32_t m0 = ((a00[wi] >> sh0) & 0x0F0F0F0Fu) | ((a01[wi] << sh1) & 0xF0F0F0F0u);
           const uint32_t m1 = ((a10[wi] >> sh0) & 0x0F0F0F0Fu) | ((a11[wi] << sh1) & 0xF0F0F0F0u);
           uint32_t av[2][4];
-          av[0][0] = *reinterpret_cast<const uint32_t*>(lut + __byte_perm(m0, vlane, 0x5504));
-          av[0][1] = *reinterpret_cast<const uint32_t*>(lut + __byte_perm(m0, vlane, 0x5514));
-          av[1][0] = *reinterpret_cast<const uint32_t*>(lut + __byte_perm(m0, vlane, 0x5524));
-          av[1][1] = *reinterpret_cast<const uint32_t*>(lut + __byte_perm(m0, vlane, 0x5534));
-          av[0][2] = *reinterpret_cast<const uint32_t*>(lut + __byte_perm(m1, vlane, 0x5504));
-          av[0][3] = *reinterpret_cast<const uint32_t*>(lut + __byte_perm(m1, vlane, 0x5514));
-          av[1][2] = *reinterpret_cast<const uint32_t*>(lut + __byte_perm(m1, vlane, 0x5524));
-          av[1][3] = *reinterpret_cast<const uint32_t*>(lut + __byte_perm(m1, vlane, 0x5534));
+          av[0][0] = lut_load(__byte_perm(m0, vlane, 0x7604));
+          av[0][1] = lut_load(__byte_perm(m0, vlane, 0x7614));
+          av[1][0] = lut_load(__byte_perm(m0, vlane, 0x7624));
+          av[1][1] = lut_load(__byte_perm(m0, vlane, 0x7634));
+          av[0][2] = lut_load(__byte_perm(m1, vlane, 0x7604));
+          av[0][3] = lut_load(__byte_perm(m1, vlane, 0x7614));
+          av[1][2] = lut_load(__byte_perm(m1, vlane, 0x7624));
+          av[1][3] = lut_load(__byte_perm(m1, vlane, 0x7634));
 #pragma unroll
           for (int e = 0; e < 2; ++e)
 #pragma unroll
@@ -497,17 +548,21 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
         for (int jn = 0; jn < 2; ++jn) mma16816(cmin[jn], ones, ones, ones, ones, mb[jn][0], mb[jn][1]);
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(smem_base + L::kEmptyBar + 8 * slot);
+    // the stage is free again: refill it with the tile STAGES ahead
+    if (!noload && k + STAGES < my_tiles) {
+      __syncwarp();
+      fence_proxy_async();
+      issue_tile(k + STAGES);
+    }
   }
 
   // ---- epilogue: warp partials -> shared memory -> CTA result ---------------------------
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-  consumer_bar_sync(cthreads);  // every tile of every warp has been consumed: the ring is free
-  float* mo = reinterpret_cast<float*>(smem + L::kMergeO);
-  float* mm = reinterpret_cast<float*>(smem + L::kMergeM);
-  float* ml = reinterpret_cast<float*>(smem + L::kMergeL);
+  __syncthreads();  // every tile of every warp has been consumed: the ring is free
+  float* mo = reinterpret_cast<float*>(gptr(L::kMergeO));
+  float* mm = reinterpret_cast<float*>(gptr(L::kMergeM));
+  float* ml = reinterpret_cast<float*>(gptr(L::kMergeL));
   if ((tig >> 1) == (gv & 1)) {
     const bool hi_tile = (gv >> 1) != 0;
     const int h0 = (2 * tig) & 3;
@@ -528,9 +583,9 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
     mm[warp * 4 + gid] = m_used;
     ml[warp * 4 + gid] = l_run;
   }
-  consumer_bar_sync(cthreads);
+  __syncthreads();
   const bool direct = S == 1 && !p.force_partial;
-  for (int idx = tid; idx < 4 * kHeadDim; idx += cthreads) {
+  for (int idx = tid; idx < 4 * kHeadDim; idx += NW * 32) {
     const int h = idx >> 7, d = idx & 127;
     if (h >= nh) continue;
     float M = -CUDART_INF_F;
@@ -563,34 +618,43 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) decode_mma_kernel(const Deco
 
 template <int NW, int STAGES>
 int launch_variant(const DecodeParams& p, cudaStream_t stream) {
-  using L = SmemLayout<NW, STAGES>;
+  using L = Smem<NW, STAGES>;
   const int gqa = p.heads_q / p.heads_kv;
   const int quads = gqa == 8 ? 2 : 1;
   const dim3 grid(p.num_splits, p.heads_kv * quads, p.batch);
-  const dim3 block((NW + 1) * 32);
+  const dim3 block(NW * 32);
   auto kern = p.stat_bf16 ? decode_mma_kernel<NW, STAGES, true> : decode_mma_kernel<NW, STAGES, false>;
   static bool configured[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[p.stat_bf16 ? 1 : 0][dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    int reserved = 0;
+    cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev);
+    if (reserved != static_cast<int>(kSmemBase)) return BKV_ERR_UNSUPPORTED;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynBytes);
     if (e != cudaSuccess) {
       set_last_cuda_error(e, "cudaFuncSetAttribute(decode_mma_kernel)");
       return BKV_ERR_CUDA;
     }
     configured[p.stat_bf16 ? 1 : 0][dev] = true;
   }
-  kern<<<grid, block, L::kTotal, stream>>>(p, quads);
+  kern<<<grid, block, L::kDynBytes, stream>>>(p, quads);
   return check_launch("bkv_decode_sm100(mma)");
 }
 
 }  // namespace
 
-int launch_decode_mma(const DecodeParams& p, cudaStream_t stream) {
-  if (p.block_size % kTile != 0 || p.block_size > 1024) return BKV_ERR_UNSUPPORTED;
+int launch_decode_mma(const DecodeParams& p, cudaStream_t stream, int config) {
+  const int r = p.block_size / kTile;
+  if (p.block_size % kTile != 0 || (r & (r - 1)) != 0 || p.block_size > 1024) return BKV_ERR_UNSUPPORTED;
   if ((p.page_stride * 4) % 16 != 0 || !aligned16(p.cache)) return BKV_ERR_UNSUPPORTED;
   if (p.token_lo % p.block_size != 0) return BKV_ERR_UNSUPPORTED;
-  return launch_variant<8, 4>(p, stream);
+  switch (config) {
+    case 1: return launch_variant<8, 4>(p, stream);
+    case 2: return launch_variant<8, 7>(p, stream);
+    case 3: return launch_variant<12, 5>(p, stream);
+    default: return launch_variant<12, 4>(p, stream);
+  }
 }
 
 int read_decode_status() {
