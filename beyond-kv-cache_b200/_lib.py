@@ -33,6 +33,8 @@ SIGNATURES = {
                          _P, _P, _P, _P, _I, _I, _I, _P, _P, _L, _L, _L, _L, _I, _P],
     "bkv_decode_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _I, _P,
                          _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "bkv_decode_noalloc_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _I, _P,
+                                 _I, _I, _I, _I, _F, _I, _P],
     "bkv_decode_device_status": [_P],
     "bkv_combine_sm100": [_P, _P, _P, _I, _L, _P, _I, _P, _P],
     "bkv_decode_range_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _P,

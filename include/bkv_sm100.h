@@ -111,6 +111,36 @@ int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const v
                      bkv_stream_t stream);
 
 /*
+ * bkv_decode_sm100 for callers that cannot allocate device memory (no counterpart in
+ * the reference, whose launcher always receives a caller-allocated workspace).
+ *
+ * Some callers have no way to provide the split workspace: code that already runs inside
+ * a stream capture, a plugin that must not touch its host's allocator, an embedder with a
+ * fixed arena.  Here the partials go to a fixed array inside the library image, so the
+ * call performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *
+ * Limits and rules:
+ *  - num_splits * batch * heads_q must not exceed BKV_NOALLOC_MAX_SPLIT_ROWS; larger
+ *    launches are refused with BKV_ERR_LIMIT.  The array costs
+ *    BKV_NOALLOC_MAX_SPLIT_ROWS * 520 bytes (about 4.1 MiB) of device memory on every GPU
+ *    that loads the library, until the process exits.
+ *  - The first call on a device looks up the array's device address (once per device, with
+ *    that device current).  Make that first call before starting any stream capture.
+ *  - All calls on one GPU share the array, which keeps the previous call's contents.  Each
+ *    call rewrites every slot it later reads, so nothing needs clearing; but two calls
+ *    whose kernels may overlap on the GPU (different streams) race on it - serialise them.
+ * Arguments and results are those of bkv_decode_sm100 without the three workspace pointers.
+ */
+#define BKV_NOALLOC_MAX_SPLIT_ROWS 8192
+int bkv_decode_noalloc_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const void* cache,
+                             int64_t num_pages, int64_t page_stride_i32, int block_size,
+                             int heads_kv, int stat_dtype, const int32_t* block_table,
+                             int64_t block_table_stride, const int32_t* seq_lens,
+                             const void* lvl_k, const void* lvl_v, int table_dtype, void* out,
+                             int out_dtype, float* out_f32, int num_splits, int batch, int heads_q,
+                             int max_seq_len, float softmax_scale, int flags, bkv_stream_t stream);
+
+/*
  * Diagnostic: reads and clears the device-side status word of the decode kernels
  * (0 = fine; 1 / 2 = a bounded wait inside the tensor-core kernel gave up after 2 s
  * instead of spinning forever).  Synchronises the device.  No counterpart in the
