@@ -45,8 +45,8 @@ FALLBACK_HBM_GBS = 6650.0
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=8192)
@@ -80,45 +80,56 @@ def ncu_traffic_bytes(workload: str):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML (read-only queries) on a
+    background thread while the timed region runs."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {
+        "hw_slowdown": 0x8,
+        "hw_thermal_slowdown": 0x40,
+        "sw_thermal_slowdown": 0x20,
+        "sw_power_cap": 0x4,
+    }
 
-    def __init__(self, index: int):
-        self.proc = None
+    def __init__(self, index: int, period_s: float = 0.005):
+        import threading
+
+        self.samples, self.reason_bits, self.max_mhz, self.error = [], 0, None, None
+        self._stop = threading.Event()
+        self._thread = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except Exception:
-            self.proc = None
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                        self.reason_bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                    except Exception as exc:  # keep the benchmark alive if a query is unsupported
+                        self.error = repr(exc)
+                        return
+                    time.sleep(period_s)
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+        except Exception as exc:
+            self.error = repr(exc)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except Exception:
-            self.proc.kill()
-            out = ""
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        reasons = sorted(name for name, bit in self.REASONS.items() if self.reason_bits & bit)
+        out = {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+               "reasons": reasons, "samples": len(self.samples)}
+        if self.error:
+            out["note"] = self.error
+        return out
 
 
 def cpu_decode_baseline(args, sample_requests: int, steps: int = 1, warmup: int = 0):
@@ -280,7 +291,7 @@ def main():
     value = world * packed_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- end-to-end serving step with host inputs --------------------------------------
-    e2e_steps = args.steps
+    e2e_steps = min(args.steps, 500)
     h_q = torch.randn((B, HEADS_Q, HEAD_DIM)).to(torch.bfloat16).pin_memory()
     h_k = torch.randn((B, HEADS_KV, HEAD_DIM)).to(torch.bfloat16).pin_memory()
     h_v = torch.randn((B, HEADS_KV, HEAD_DIM)).to(torch.bfloat16).pin_memory()

@@ -1,0 +1,132 @@
+"""Multi-GPU forms of the packed decode path (one process per GPU, ``torch.distributed``).
+
+The reference has no multi-GPU decode (its serving numbers are single-GPU; tensor
+parallelism is delegated to vLLM).  Two shardings are provided here:
+
+* **Request-batch sharding** — requests are independent, so every rank owns a slice of
+  the batch with its own page pool; there is no collective on the data path
+  (:func:`shard_requests`).
+* **KV-range split of one long sequence** — rank ``r`` owns a contiguous, page-aligned
+  range of positions, runs the decode kernel over it and produces an un-normalised
+  partial ``(o, m, l)`` per (request, query head); the partials (16.6 KB per rank for 32
+  heads) are all-gathered and merged with the log-sum-exp combine kernel, "splits =
+  world size" (:func:`decode_kv_range_split`).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .quant.beyond_cute import PagedLayout
+
+
+def shard_requests(batch: int, world: int, rank: int) -> range:
+    """Contiguous, balanced slice of ``range(batch)`` owned by ``rank`` (sizes differ by
+    at most one; the first ``batch % world`` ranks get the extra request)."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    base, extra = divmod(int(batch), world)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def kv_range_for_rank(seq_len: int, block_size: int, world: int, rank: int) -> tuple[int, int]:
+    """Positions ``[lo, hi)`` of a ``seq_len``-token sequence owned by ``rank``: pages
+    are dealt in contiguous, balanced runs so every boundary is page-aligned; the last
+    non-empty range ends at ``seq_len``.  Ranks beyond the page count get ``(x, x)``."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError("rank must be in [0, world)")
+    pages = (int(seq_len) + block_size - 1) // block_size
+    pr = shard_requests(pages, world, rank)
+    lo = pr.start * block_size
+    hi = max(lo, min(pr.stop * block_size, int(seq_len)))
+    return lo, hi
+
+
+def gather_partials(o: torch.Tensor, m: torch.Tensor, l: torch.Tensor, group=None):
+    """All-gather the per-rank partials: returns ``(world, rows, 128)``, ``(world, rows)``,
+    ``(world, rows)`` tensors (any backend; NCCL on GPUs, gloo in the CPU tests)."""
+    world = dist.get_world_size(group)
+    packed = torch.cat([o.reshape(o.shape[0], -1), m.reshape(-1, 1), l.reshape(-1, 1)], dim=1).contiguous()
+    flat = torch.empty((world * packed.shape[0], packed.shape[1]), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(flat, packed, group=group)  # rank-major concatenation along dim 0
+    out = flat.view(world, packed.shape[0], packed.shape[1])
+    d = o.shape[-1]
+    return out[:, :, :d].contiguous(), out[:, :, d].contiguous(), out[:, :, d + 1].contiguous()
+
+
+def decode_range_partial(
+    q: torch.Tensor,
+    cache: torch.Tensor,
+    layout: PagedLayout,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    q_points_k: torch.Tensor,
+    q_points_v: torch.Tensor,
+    *,
+    token_lo: int,
+    token_hi: int,
+    softmax_scale: float,
+    stat_dtype: Optional[torch.dtype] = None,
+):
+    """Un-normalised attention of every request over positions ``[token_lo, token_hi)``
+    (clipped to its ``seq_len``): ``o (rows,128)``, ``m (rows,)`` natural-log maximum,
+    ``l (rows,)`` sum, all float32, rows = batch * query heads."""
+    batch, heads_q = int(q.shape[0]), int(q.shape[1])
+    rows = batch * heads_q
+    o = torch.empty((rows, 128), dtype=torch.float32, device=q.device)
+    m = torch.empty((rows,), dtype=torch.float32, device=q.device)
+    l = torch.empty((rows,), dtype=torch.float32, device=q.device)
+    if q_points_k.dtype != q_points_v.dtype:
+        q_points_k, q_points_v = q_points_k.float(), q_points_v.float()
+    stat = stat_dtype if stat_dtype is not None else q.dtype
+    _lib.call(
+        "bkv_decode_range_sm100",
+        q.data_ptr(), q.stride(0), _lib.dtype_code(q.dtype),
+        cache.data_ptr(), int(cache.shape[0]), int(cache.stride(0)), int(layout.block_size),
+        int(layout.num_kv_heads), _lib.dtype_code(stat),
+        block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
+        q_points_k.contiguous().data_ptr(), q_points_v.contiguous().data_ptr(), _lib.dtype_code(q_points_k.dtype),
+        o.data_ptr(), m.data_ptr(), l.data_ptr(), batch, heads_q, int(token_lo), int(token_hi),
+        float(softmax_scale), 0, _lib.current_stream(q.device),
+    )
+    return o, m, l
+
+
+def decode_kv_range_split(
+    q: torch.Tensor,
+    cache: torch.Tensor,
+    layout: PagedLayout,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    q_points_k: torch.Tensor,
+    q_points_v: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    token_lo: int,
+    token_hi: int,
+    softmax_scale: float,
+    stat_dtype: Optional[torch.dtype] = None,
+    group=None,
+) -> torch.Tensor:
+    """Decode attention of a batch whose KV positions are split across the ranks of
+    ``group``: this rank attends ``[token_lo, token_hi)`` from its own pages, the partials
+    are all-gathered (NCCL over NVLink) and merged on every rank into ``out``
+    ``(batch, heads_q, 128)``.  ``q`` must be identical on all ranks."""
+    o, m, l = decode_range_partial(
+        q, cache, layout, block_table, seq_lens, q_points_k, q_points_v,
+        token_lo=token_lo, token_hi=token_hi, softmax_scale=softmax_scale, stat_dtype=stat_dtype,
+    )
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        o_all, m_all, l_all = gather_partials(o, m, l, group)
+    else:
+        o_all, m_all, l_all = o.unsqueeze(0), m.unsqueeze(0), l.unsqueeze(0)
+    _lib.call(
+        "bkv_combine_sm100", o_all.data_ptr(), m_all.data_ptr(), l_all.data_ptr(), int(o_all.shape[0]),
+        int(o_all.shape[1]), out.data_ptr(), _lib.dtype_code(out.dtype), None, _lib.current_stream(q.device),
+    )
+    return out
