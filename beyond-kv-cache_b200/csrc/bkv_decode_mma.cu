@@ -26,6 +26,8 @@
 // makes every 128-bit code load of a quarter-warp hit eight distinct bank groups.
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "bkv_decode_common.cuh"
 
 namespace bkv {
@@ -54,6 +56,8 @@ constexpr uint32_t kTok0 = 0xEFDC2310u;  // 0,1,3,2,12,13,15,14
 constexpr uint32_t kTok1 = 0x6754AB98u;  // 8,9,11,10,4,5,7,6
 
 constexpr int BKV_FLAG_DEBUG_NOLOAD = 0x100;  // timing experiment: reuse the first ring fill
+constexpr int BKV_FLAG_DEBUG_NOCOPY = 0x400;  // timing experiment: run the issue logic without the copies
+constexpr int BKV_FLAG_DEBUG_NOWAIT = 0x200;  // timing experiment: issue loads but never wait for them
 
 // ---- PTX helpers --------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -190,9 +194,14 @@ struct Smem {
 };
 
 // registers a thread may use when one CTA of NW warps owns the SM (64 K registers, allocated in eights)
-constexpr int max_regs_for(int nw) { return (65536 / (nw * 32)) / 8 * 8 > 255 ? 255 : (65536 / (nw * 32)) / 8 * 8; }
+constexpr int max_regs_for(int nw) {
+  // the register file is split over the four schedulers (16 K registers each) and a CTA's
+  // warps are dealt to them round-robin
+  const int per_thread = 16384 / (((nw + 3) / 4) * 32) / 8 * 8;
+  return per_thread > 255 ? 255 : per_thread;
+}
 
-template <int NW, int STAGES, bool STAT_BF16>
+template <int NW, int STAGES, bool STAT_BF16, int ABL = 0>
 __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodeParams p, const int quads) {
   using L = Smem<NW, STAGES>;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -216,6 +225,8 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
   const int log2r = 31 - __clz(BS / kTile);  // tiles per page is a power of two
   const int tiles_per_page = 1 << log2r;
   const bool noload = (p.flags & BKV_FLAG_DEBUG_NOLOAD) != 0;
+  const bool nocopy = (p.flags & BKV_FLAG_DEBUG_NOCOPY) != 0;
+  const bool nowait = (p.flags & BKV_FLAG_DEBUG_NOWAIT) != 0 || nocopy;
 
   if (p.flags & BKV_FLAG_PDL_WAIT) pdl_wait();
 
@@ -288,9 +299,9 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
     if (bad) phys = 0;
     const uint32_t sub = (warp + ki * NW) & (tiles_per_page - 1);
     const uint32_t full = L::kFullBar + 8 * slot;
-    if (lane == 0) mbar_arrive_expect_tx(full, 2560);
+    if (lane == 0 && !(nocopy && ki >= STAGES)) mbar_arrive_expect_tx(full, 2560);
     __syncwarp();
-    if (lane < n_chunks)
+    if (lane < n_chunks && !(nocopy && ki >= STAGES))
       bulk_copy_g2s(slot_addr(slot) + ch_dst, src_base + phys * page_bytes + sub * ch_sub, ch_bytes, full);
   };
   {
@@ -387,116 +398,150 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
     for (int c = 0; c < 4; ++c) cmin[jn][c] = 0.f;
   float m_used = -CUDART_INF_F, l_run = 0.f;
 
-  for (int k = 0; k < my_tiles; ++k) {
-    const int use = k / STAGES;
-    const int stage = k - use * STAGES;
-    const int slot = warp * STAGES + stage;
-    if (!(noload && use > 0)) {
-      const uint32_t full = L::kFullBar + 8 * slot;
-      WaitBudget budget;
-      bool gave_up = false;
-      while (!mbar_try_wait(full, use & 1)) {
-        if (__any_sync(0xffffffffu, budget.expired())) {
-          gave_up = true;
-          break;
-        }
-      }
-      if (gave_up) {
+  // ---- main loop: two ring tiles (32 tokens) per iteration -------------------------------
+  auto wait_tile = [&](int k) -> bool {  // false: the bounded wait gave up
+    const int use = k / STAGES, stage = k - use * STAGES;
+    if ((noload || nowait) && use > 0) return true;
+    const uint32_t full = L::kFullBar + 8 * (warp * STAGES + stage);
+    WaitBudget budget;
+    while (!mbar_try_wait(full, use & 1)) {
+      if (__any_sync(0xffffffffu, budget.expired())) {
         atomicExch(&g_decode_status, 2);
-        break;
+        return false;
       }
     }
+    return true;
+  };
+  auto tile_len = [&](int k) -> int {  // valid tokens of ring tile k (0: none / unmapped page)
+    if (k >= my_tiles) return 0;
     const int j = warp + k * NW;
     const int tok0 = (page_lo + split + S * (j >> log2r)) * BS + (j & (tiles_per_page - 1)) * kTile;
-    const int nv = (bad_slots >> stage) & 1 ? 0 : min(kTile, hi - tok0);
-    const uint32_t sb = slot_addr(slot);
-    if (nv > 0) {
-      // ------------------------------ S^T = Q * Lk^T -------------------------------------
-      float sacc[2][4];
+    return (bad_slots >> (k % STAGES)) & 1 ? 0 : min(kTile, hi - tok0);
+  };
+
+  // timing ablations (ABL): bit 0 drops the MMAs, bit 1 replaces table look-ups by their address
+#define BKV_MMA(c, a0, a1, a2, a3, b0, b1) \
+  do { if (ABL & 1) { asm volatile("" ::"r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1)); } else { mma16816(c, a0, a1, a2, a3, b0, b1); } } while (0)
+#define BKV_LUT(a) ((ABL & 2) ? (a) : lut_load(a))
+  auto process_pair = [&](auto partial_tag, const uint32_t sbA, const uint32_t sbB, const int nvA, const int nvB) {
+    constexpr bool PARTIAL = decltype(partial_tag)::value;
+    const uint32_t sb[2] = {sbA, sbB};
+    const int nv[2] = {nvA, nvB};
+    // ------------------------------ S^T = Q * Lk^T (4 independent accumulator chains) ------
+    float sacc[2][2][4] = {};
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
 #pragma unroll
       for (int o = 0; o < 2; ++o) {
-        const uint4 kw = ring_load128(sb + (o ? kc_off1 : kc_off0));
+        const uint4 kw = ring_load128(sb[t] + (o ? kc_off1 : kc_off0));
         const uint32_t w4[4] = {kw.x, kw.y, kw.z, kw.w};
+        // all 16 look-up addresses first, then the 16 look-ups, then the 8 dependent MMAs
+        uint32_t ad[8][2], bv[8][2];
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
-          const uint32_t wd = w4[jj >> 1];
-          const uint32_t b0 = lut_load(__byte_perm(wd, klane, (jj & 1) ? 0x7624 : 0x7604));
-          const uint32_t b1 = lut_load(__byte_perm(wd, klane, (jj & 1) ? 0x7634 : 0x7614));
-          if (jj == 0) mma16816_zero(sacc[o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], b0, b1);
-          else mma16816(sacc[o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], b0, b1);
+          ad[jj][0] = __byte_perm(w4[jj >> 1], klane, (jj & 1) ? 0x7624 : 0x7604);
+          ad[jj][1] = __byte_perm(w4[jj >> 1], klane, (jj & 1) ? 0x7634 : 0x7614);
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          bv[jj][0] = BKV_LUT(ad[jj][0]);
+          bv[jj][1] = BKV_LUT(ad[jj][1]);
+        }
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          if (jj == 0 && !(ABL & 1)) mma16816_zero(sacc[t][o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], bv[jj][0], bv[jj][1]);
+          else BKV_MMA(sacc[t][o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], bv[jj][0], bv[jj][1]);
         }
       }
-      // ------------------------------ scores of this lane ---------------------------------
-      float s[2][2];
+    // ------------------------------ V index bytes (token pair -> one table index) -----------
+    // Independent of the softmax below, so issued here to overlap with its latency.
+    uint32_t vidx[2][2][4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
 #pragma unroll
       for (int o = 0; o < 2; ++o) {
-        const uint2 st0 = ring_load64<0>(sb + ks_off[o][0]);
-        const uint2 st1 = ring_load64<0>(sb + ks_off[o][1]);
+        const uint4 xf = ring_load128(sb[t] + vc_off[o][0]);
+        const uint4 xs = ring_load128(sb[t] + vc_off[o][1]);
+        vidx[t][o][0] = ((xf.x >> sh0) & 0x0F0F0F0Fu) | ((xs.x << sh1) & 0xF0F0F0F0u);
+        vidx[t][o][1] = ((xf.y >> sh0) & 0x0F0F0F0Fu) | ((xs.y << sh1) & 0xF0F0F0F0u);
+        vidx[t][o][2] = ((xf.z >> sh0) & 0x0F0F0F0Fu) | ((xs.z << sh1) & 0xF0F0F0F0u);
+        vidx[t][o][3] = ((xf.w >> sh0) & 0x0F0F0F0Fu) | ((xs.w << sh1) & 0xF0F0F0F0u);
+      }
+    // ------------------------------ scores of this lane -------------------------------------
+    float s[2][2][2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int o = 0; o < 2; ++o) {
+        const uint2 st0 = ring_load64<0>(sb[t] + ks_off[o][0]);
+        const uint2 st1 = ring_load64<0>(sb[t] + ks_off[o][1]);
         const float2 a0 = stat_word_to_f32<STAT_BF16>(st0.x), b0 = stat_word_to_f32<STAT_BF16>(st0.y);
         const float2 a1 = stat_word_to_f32<STAT_BF16>(st1.x), b1 = stat_word_to_f32<STAT_BF16>(st1.y);
-        float p0 = a0.x * sacc[o][0];
+        float p0 = a0.x * sacc[t][o][0];
         p0 = fmaf(a0.y, qs0, p0);
-        p0 = fmaf(b0.x, sacc[o][2], p0);
+        p0 = fmaf(b0.x, sacc[t][o][2], p0);
         p0 = fmaf(b0.y, qs1, p0);
-        float p1 = a1.x * sacc[o][1];
+        float p1 = a1.x * sacc[t][o][1];
         p1 = fmaf(a1.y, qs0, p1);
-        p1 = fmaf(b1.x, sacc[o][3], p1);
+        p1 = fmaf(b1.x, sacc[t][o][3], p1);
         p1 = fmaf(b1.y, qs1, p1);
         p0 += __shfl_xor_sync(0xffffffffu, p0, 16);
         p1 += __shfl_xor_sync(0xffffffffu, p1, 16);
-        s[o][0] = p0;
-        s[o][1] = p1;
+        if (PARTIAL) {  // tokens behind the end of the sequence (their statistics may be NaN)
+          if (tk[o][0] >= nv[t]) p0 = -CUDART_INF_F;
+          if (tk[o][1] >= nv[t]) p1 = -CUDART_INF_F;
+        }
+        s[t][o][0] = p0;
+        s[t][o][1] = p1;
       }
-      if (nv < kTile) {
+    // ------------------------------ online softmax over the 32 tokens -----------------------
+    float tmax = fmaxf(fmaxf(fmaxf(s[0][0][0], s[0][0][1]), fmaxf(s[0][1][0], s[0][1][1])),
+                       fmaxf(fmaxf(s[1][0][0], s[1][0][1]), fmaxf(s[1][1][0], s[1][1][1])));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+    const bool need = tmax > m_used + kRescaleThreshold;
+    if (__any_sync(0xffffffffu, need)) {
+      const float m_new = need ? tmax : m_used;
+      const float corr = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_used - m_new);
+      m_used = m_new;
+      l_run *= corr;
+      const float ce = __shfl_sync(0xffffffffu, corr, ((2 * tig) & 3) * 4);
+      const float co = __shfl_sync(0xffffffffu, corr, ((2 * tig + 1) & 3) * 4);
 #pragma unroll
-        for (int o = 0; o < 2; ++o)
-#pragma unroll
-          for (int e = 0; e < 2; ++e)
-            if (tk[o][e] >= nv) s[o][e] = -CUDART_INF_F;
-      }
-      // ------------------------------ online softmax --------------------------------------
-      float tmax = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-      const bool need = tmax > m_used + kRescaleThreshold;
-      if (__any_sync(0xffffffffu, need)) {
-        const float m_new = need ? tmax : m_used;
-        const float corr = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_used - m_new);
-        m_used = m_new;
-        l_run *= corr;
-        const float ce = __shfl_sync(0xffffffffu, corr, ((2 * tig) & 3) * 4);
-        const float co = __shfl_sync(0xffffffffu, corr, ((2 * tig + 1) & 3) * 4);
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-          for (int jn = 0; jn < 2; ++jn) {
-            oacc[i][jn][0] *= ce;
-            oacc[i][jn][1] *= co;
-            oacc[i][jn][2] *= ce;
-            oacc[i][jn][3] *= co;
-          }
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int jn = 0; jn < 2; ++jn) {
-          cmin[jn][0] *= ce;
-          cmin[jn][1] *= co;
-          cmin[jn][2] *= ce;
-          cmin[jn][3] *= co;
+          oacc[i][jn][0] *= ce;
+          oacc[i][jn][1] *= co;
+          oacc[i][jn][2] *= ce;
+          oacc[i][jn][3] *= co;
         }
-      }
-      uint32_t ph[2];
-#pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const float e0 = fast_exp2(s[o][0] - m_used), e1 = fast_exp2(s[o][1] - m_used);
-        l_run += e0 + e1;
-        ph[o] = pack_half2(e0, e1);
-      }
-      // ------------------------------ W = p * scale_v, p * min_v ---------------------------
-      uint32_t wb[2][2], mb[2][2];
 #pragma unroll
       for (int jn = 0; jn < 2; ++jn) {
+        cmin[jn][0] *= ce;
+        cmin[jn][1] *= co;
+        cmin[jn][2] *= ce;
+        cmin[jn][3] *= co;
+      }
+    }
+    uint32_t ph[2][2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int o = 0; o < 2; ++o) {
+        const float e0 = fast_exp2(s[t][o][0] - m_used), e1 = fast_exp2(s[t][o][1] - m_used);
+        l_run += e0 + e1;
+        ph[t][o] = pack_half2(e0, e1);
+      }
+    // ------------------------------ per tile: W = p*scale_v, p*min_v, then O += Lv^T * W ----
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      uint32_t wb[2][2], mb[2][2];
+#pragma unroll
+      for (int jn = 0; jn < 2; ++jn)
 #pragma unroll
         for (int o = 0; o < 2; ++o) {
-          const uint2 vs = jn ? ring_load64<2 * kTile * 4>(sb + vs_off[o]) : ring_load64<0>(sb + vs_off[o]);
+          const uint2 vs = jn ? ring_load64<2 * kTile * 4>(sb[t] + vs_off[o]) : ring_load64<0>(sb[t] + vs_off[o]);
           uint32_t sc2, mn2;
           if (STAT_BF16) {
             const uint32_t first = pair_swapped ? vs.y : vs.x, second = pair_swapped ? vs.x : vs.y;
@@ -506,53 +551,62 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
             sc2 = __byte_perm(vs.x, vs.y, sel_scale);
             mn2 = __byte_perm(vs.x, vs.y, sel_min);
           }
-          uint32_t wv = hmul2_u32(ph[o], sc2), mv = hmul2_u32(ph[o], mn2);
-          if (nv < kTile) {  // stale statistics behind the last token may be NaN/Inf
-            const uint32_t keep = (tk[o][0] < nv ? 0x0000FFFFu : 0u) | (tk[o][1] < nv ? 0xFFFF0000u : 0u);
+          uint32_t wv = hmul2_u32(ph[t][o], sc2), mv = hmul2_u32(ph[t][o], mn2);
+          if (PARTIAL) {  // 0 * NaN would poison the accumulators
+            const uint32_t keep = (tk[o][0] < nv[t] ? 0x0000FFFFu : 0u) | (tk[o][1] < nv[t] ? 0xFFFF0000u : 0u);
             wv &= keep;
             mv &= keep;
           }
           wb[jn][o] = wv;
           mb[jn][o] = mv;
         }
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+        const uint32_t m0 = vidx[t][0][wi], m1 = vidx[t][1][wi];
+        uint32_t aa[8], av[2][4];
+        aa[0] = __byte_perm(m0, vlane, 0x7604);
+        aa[1] = __byte_perm(m0, vlane, 0x7614);
+        aa[2] = __byte_perm(m0, vlane, 0x7624);
+        aa[3] = __byte_perm(m0, vlane, 0x7634);
+        aa[4] = __byte_perm(m1, vlane, 0x7604);
+        aa[5] = __byte_perm(m1, vlane, 0x7614);
+        aa[6] = __byte_perm(m1, vlane, 0x7624);
+        aa[7] = __byte_perm(m1, vlane, 0x7634);
+        av[0][0] = BKV_LUT(aa[0]);
+        av[0][1] = BKV_LUT(aa[1]);
+        av[1][0] = BKV_LUT(aa[2]);
+        av[1][1] = BKV_LUT(aa[3]);
+        av[0][2] = BKV_LUT(aa[4]);
+        av[0][3] = BKV_LUT(aa[5]);
+        av[1][2] = BKV_LUT(aa[6]);
+        av[1][3] = BKV_LUT(aa[7]);
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+#pragma unroll
+          for (int jn = 0; jn < 2; ++jn)
+            BKV_MMA(oacc[2 * wi + e][jn], av[e][0], av[e][1], av[e][2], av[e][3], wb[jn][0], wb[jn][1]);
       }
-      // ------------------------------ O += Lv^T * W ---------------------------------------
-      {
-        const uint4 x00 = ring_load128(sb + vc_off[0][0]);
-        const uint4 x01 = ring_load128(sb + vc_off[0][1]);
-        const uint4 x10 = ring_load128(sb + vc_off[1][0]);
-        const uint4 x11 = ring_load128(sb + vc_off[1][1]);
-        const uint32_t a00[4] = {x00.x, x00.y, x00.z, x00.w}, a01[4] = {x01.x, x01.y, x01.z, x01.w};
-        const uint32_t a10[4] = {x10.x, x10.y, x10.z, x10.w}, a11[4] = {x11.x, x11.y, x11.z, x11.w};
+      const uint32_t ones = 0x3C003C00u;
 #pragma unroll
-        for (int wi = 0; wi < 4; ++wi) {
-          const uint32_t m0 = ((a00[wi] >> sh0) & 0x0F0F0F0Fu) | ((a01[wi] << sh1) & 0xF0F0F0F0u);
-          const uint32_t m1 = ((a10[wi] >> sh0) & 0x0F0F0F0Fu) | ((a11[wi] << sh1) & 0xF0F0F0F0u);
-          uint32_t av[2][4];
-          av[0][0] = lut_load(__byte_perm(m0, vlane, 0x7604));
-          av[0][1] = lut_load(__byte_perm(m0, vlane, 0x7614));
-          av[1][0] = lut_load(__byte_perm(m0, vlane, 0x7624));
-          av[1][1] = lut_load(__byte_perm(m0, vlane, 0x7634));
-          av[0][2] = lut_load(__byte_perm(m1, vlane, 0x7604));
-          av[0][3] = lut_load(__byte_perm(m1, vlane, 0x7614));
-          av[1][2] = lut_load(__byte_perm(m1, vlane, 0x7624));
-          av[1][3] = lut_load(__byte_perm(m1, vlane, 0x7634));
-#pragma unroll
-          for (int e = 0; e < 2; ++e)
-#pragma unroll
-            for (int jn = 0; jn < 2; ++jn)
-              mma16816(oacc[2 * wi + e][jn], av[e][0], av[e][1], av[e][2], av[e][3], wb[jn][0], wb[jn][1]);
-        }
-        const uint32_t ones = 0x3C003C00u;
-#pragma unroll
-        for (int jn = 0; jn < 2; ++jn) mma16816(cmin[jn], ones, ones, ones, ones, mb[jn][0], mb[jn][1]);
-      }
+      for (int jn = 0; jn < 2; ++jn) BKV_MMA(cmin[jn], ones, ones, ones, ones, mb[jn][0], mb[jn][1]);
     }
-    // the stage is free again: refill it with the tile STAGES ahead
+  };
+
+  for (int k = 0; k < my_tiles; k += 2) {
+    if (!wait_tile(k)) break;
+    const bool has_b = k + 1 < my_tiles;
+    if (has_b && !wait_tile(k + 1)) break;
+    const int nvA = tile_len(k), nvB = tile_len(k + 1);
+    const uint32_t sbA = slot_addr(warp * STAGES + k % STAGES);
+    const uint32_t sbB = slot_addr(warp * STAGES + (k + 1) % STAGES);
+    if (nvA == kTile && nvB == kTile) process_pair(std::false_type{}, sbA, sbB, nvA, nvB);
+    else if (nvA > 0 || nvB > 0) process_pair(std::true_type{}, sbA, sbB, nvA, nvB);
+    // both stages are free again: refill them with the tiles STAGES ahead
     if (!noload && k + STAGES < my_tiles) {
       __syncwarp();
       fence_proxy_async();
       issue_tile(k + STAGES);
+      if (k + 1 + STAGES < my_tiles) issue_tile(k + 1 + STAGES);
     }
   }
 
@@ -616,14 +670,14 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
   }
 }
 
-template <int NW, int STAGES>
+template <int NW, int STAGES, int ABL = 0>
 int launch_variant(const DecodeParams& p, cudaStream_t stream) {
   using L = Smem<NW, STAGES>;
   const int gqa = p.heads_q / p.heads_kv;
   const int quads = gqa == 8 ? 2 : 1;
   const dim3 grid(p.num_splits, p.heads_kv * quads, p.batch);
   const dim3 block(NW * 32);
-  auto kern = p.stat_bf16 ? decode_mma_kernel<NW, STAGES, true> : decode_mma_kernel<NW, STAGES, false>;
+  auto kern = p.stat_bf16 ? decode_mma_kernel<NW, STAGES, true, ABL> : decode_mma_kernel<NW, STAGES, false, ABL>;
   static bool configured[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -651,9 +705,14 @@ int launch_decode_mma(const DecodeParams& p, cudaStream_t stream, int config) {
   if (p.token_lo % p.block_size != 0) return BKV_ERR_UNSUPPORTED;
   switch (config) {
     case 1: return launch_variant<8, 4>(p, stream);
-    case 2: return launch_variant<8, 7>(p, stream);
+    case 2: return launch_variant<8, 6>(p, stream);
     case 3: return launch_variant<12, 5>(p, stream);
-    default: return launch_variant<12, 4>(p, stream);
+    case 4: return launch_variant<16, 3>(p, stream);
+    case 5: return launch_variant<12, 4>(p, stream);
+    case 10: return launch_variant<8, 4, 1>(p, stream);
+    case 11: return launch_variant<8, 4, 2>(p, stream);
+    case 12: return launch_variant<8, 4, 3>(p, stream);
+    default: return launch_variant<8, 4>(p, stream);
   }
 }
 
