@@ -12,18 +12,21 @@
 // register; the per-(token, group) scale and minimum are applied outside the MMAs:
 //   s[t,h]  = sum_g  scale_k[t,g] * (sum_{d in g} q[h,d] * Lk_g[code_k[t,d]]) + min_k[t,g] * sum_{d in g} q[h,d]
 //   o[h,d]  = sum_t (p[t,h] * scale_v[t,g(d)]) * Lv_g(d)[code_v[t,d]]  +  sum_t p[t,h] * min_v[t,g(d)]
-// The byte table is replicated so that lane l only ever reads shared-memory bank l
-// (bank l holds a copy of the table of K group l%4, and of V group l/8): every table
-// look-up is conflict-free.  MMA fragments are laid out so that each lane only needs
-// levels of "its" group:
-//   QK : S^T[(h,g), token] = Q_blockdiag[(h,g), d] * Lk[d, token]   (k-slots of lane tig belong to group tig)
-//   PV : O[d, (h,g')]      = Lv^T[d, token] * (p*scale_v)[token, (h,g')]   (rows of lane gid belong to group gid/2)
-// Products whose row group and column group differ are computed and discarded.
+// The byte tables are replicated so that lane l only ever reads shared-memory bank l, which
+// makes every look-up conflict-free.  An MMA works on one PAIR of groups {P, P+2} (P = 0, 1);
+// bank l of table block P holds the K table of the group lane l feeds into the QK MMAs of
+// pair P, and the V table of the group lane l feeds into the PV MMAs of pair P:
+//   QK : S[token, (h, g)]  = Lk[token, d] * Q_blockdiag[d, (h, g)]        (k-slots of lane tig: group 2*(tig/2)+P)
+//   PV : O[d, (h, g')]     = Lv^T[d, token] * (p*scale_v)[token, (h, g')]  (rows of lane gid:  group 2*(gid/4)+P)
+// Half of the products pair a d with a column of the other group of the pair and are discarded.
+// The probabilities leave the QK accumulators with tokens spread over gid and are handed to the
+// PV operand layout (tokens spread over tig) with two shuffles per tile.
 //
-// The table sits at the fixed shared-memory address 0x10000, so a look-up address is a
-// single byte-permute of (code word, lane constant) with no addition.  Tokens of a tile
-// are assigned to MMA columns / k-slots through a fixed permutation (kTok0 / kTok1) that
-// makes every 128-bit code load of a quarter-warp hit eight distinct bank groups.
+// The tables sit at the fixed shared-memory addresses 0x10000 / 0x20000, so a look-up address
+// is a single byte-permute of (code word, lane constant) with no addition.  Tokens of a tile are
+// assigned to MMA rows / k-slots through fixed permutations (kTokOfSlot, kRowSlot) which,
+// together with a 16-byte skew of the second half of the code chunks, make every 64-bit code
+// load of a half-warp conflict-free.
 #include <math_constants.h>
 
 #include <type_traits>
@@ -37,23 +40,30 @@ __device__ int g_decode_status = 0;  // non-zero: 1/2 a bounded wait gave up, 3 
 namespace {
 
 constexpr int kTile = 16;
-constexpr int kTileBytes = 2592;
-constexpr int kOffKCode = 0;
-constexpr int kOffKStat = 1024;
-constexpr int kOffVCode = 1280;   // tokens 0-7; tokens 8-15 start 32 bytes later than contiguous
-constexpr int kVCodeSkew = 32;
-constexpr int kOffVStat = 2336;
+// one ring tile: code chunks of tokens 8-15 start kCodeSkew bytes later than contiguous
+constexpr int kCodeSkew = 16;
+constexpr int kOffKLo = 0;
+constexpr int kOffKHi = 512 + kCodeSkew;
+constexpr int kOffKStat = kOffKHi + 512;
+constexpr int kOffVLo = kOffKStat + 256;
+constexpr int kOffVHi = kOffVLo + 512 + kCodeSkew;
+constexpr int kOffVStat = kOffVHi + 512;
+constexpr int kTileBytes = kOffVStat + 256;  // 2592
 constexpr uint32_t kSmemBase = 0x400;   // dynamic shared memory starts after the 1 KB the system reserves
-constexpr uint32_t kLutAddr = 0x10000;  // 64 KB table, 64 KB aligned: address = 0x10000 | byte << 8 | slot
-constexpr uint32_t kRingHi = 0x20000;
-constexpr int kCtrlBytes = 2048;        // barriers, tile lengths, fp16 level tables
+constexpr uint32_t kSmemEnd = kSmemBase + 232448;  // 227 KB opt-in maximum
+constexpr uint32_t kLutAddr = 0x10000;  // table block P at kLutAddr + P*kLutBlock: address = block | byte << 8 | slot
+constexpr uint32_t kLutBlock = 0x10000;
+constexpr uint32_t kRingHi = kLutAddr + 2 * kLutBlock;
+constexpr int kCtrlBytes = 2048;        // barriers, fp16 level tables
 constexpr uint32_t kRingLo = kSmemBase + kCtrlBytes;
 constexpr int kLoSlots = (kLutAddr - kRingLo) / kTileBytes;
+constexpr int kHiSlots = (kSmemEnd - kRingHi) / kTileBytes;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait that lasts 2 s gives up
 constexpr float kRescaleThreshold = 8.f;                     // log2 units: p stays below 2^8
-// token held by MMA column / k-slot n of the first (kTok0) and second (kTok1) half of a tile
-constexpr uint32_t kTok0 = 0xEFDC2310u;  // 0,1,3,2,12,13,15,14
-constexpr uint32_t kTok1 = 0x6754AB98u;  // 8,9,11,10,4,5,7,6
+// token held by k-slot n of the PV MMAs (nibble n): 0,1,3,2, 8,9,11,10, 4,5,7,6, 12,13,15,14
+constexpr unsigned long long kTokOfSlot = 0xEFDC6754AB982310ull;
+// QK MMA row g (and g+8) carries the token of k-slot kRowSlot[g] (and +8): 0,1,4,5,2,3,6,7 (an involution)
+constexpr uint32_t kRowSlot = 0x76325410u;
 
 constexpr int BKV_FLAG_DEBUG_NOLOAD = 0x100;  // timing experiment: reuse the first ring fill
 constexpr int BKV_FLAG_DEBUG_NOCOPY = 0x400;  // timing experiment: run the issue logic without the copies
@@ -176,24 +186,7 @@ __device__ __forceinline__ uint32_t slot_addr(int slot) {
   return slot < kLoSlots ? kRingLo + slot * kTileBytes : kRingHi + (slot - kLoSlots) * kTileBytes;
 }
 
-template <int NW, int STAGES>
-struct Smem {
-  static constexpr int kSlots = NW * STAGES;
-  static_assert(kSlots <= 64, "control block holds at most 64 ring slots");
-  static constexpr uint32_t kFullBar = kSmemBase;        // 8 B each
-  static constexpr uint32_t kLevels = kSmemBase + 1280;  // fp16 [K|V][4][16]
-  static constexpr int kMergeBytes = NW * 4 * kHeadDim * 4 + NW * 4 * 4 * 2;
-  static constexpr int kHiSlots = kSlots > kLoSlots ? kSlots - kLoSlots : 0;
-  static constexpr int kHiBytes = kHiSlots * kTileBytes > kMergeBytes ? kHiSlots * kTileBytes : kMergeBytes;
-  static constexpr int kDynBytes = static_cast<int>(kRingHi - kSmemBase) + kHiBytes;
-  static_assert(kDynBytes <= 232448, "exceeds the 227 KB a CTA can opt into");
-  // epilogue overlay in the high region (all ring traffic has drained by then)
-  static constexpr uint32_t kMergeO = kRingHi;
-  static constexpr uint32_t kMergeM = kMergeO + NW * 4 * kHeadDim * 4;
-  static constexpr uint32_t kMergeL = kMergeM + NW * 4 * 4;
-};
-
-// registers a thread may use when one CTA of NW warps owns the SM (64 K registers, allocated in eights)
+// registers a thread may use when one CTA of NW warps owns the SM
 constexpr int max_regs_for(int nw) {
   // the register file is split over the four schedulers (16 K registers each) and a CTA's
   // warps are dealt to them round-robin
@@ -201,12 +194,27 @@ constexpr int max_regs_for(int nw) {
   return per_thread > 255 ? 255 : per_thread;
 }
 
+template <int NW, int STAGES>
+struct Smem {
+  static constexpr int kSlots = NW * STAGES;
+  static_assert(kSlots <= kLoSlots + kHiSlots, "ring does not fit next to the two table blocks");
+  static_assert(kSlots <= 64, "control block holds at most 64 barriers");
+  static constexpr uint32_t kFullBar = kSmemBase;        // 8 B each
+  static constexpr uint32_t kLevels = kSmemBase + 1280;  // fp16 [K|V][4][16]
+  static constexpr int kDynBytes = static_cast<int>(kSmemEnd - kSmemBase);
+  // epilogue overlay in the high region (all ring traffic has drained by then)
+  static constexpr uint32_t kMergeO = kRingHi;
+  static constexpr uint32_t kMergeM = kMergeO + NW * 4 * kHeadDim * 4;
+  static constexpr uint32_t kMergeL = kMergeM + NW * 4 * 4;
+  static_assert(kMergeL + NW * 4 * 4 <= kSmemEnd, "merge overlay must fit in the high region");
+};
+
 template <int NW, int STAGES, bool STAT_BF16, int ABL = 0>
 __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodeParams p, const int quads) {
   using L = Smem<NW, STAGES>;
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t smem_base = smem_u32(smem);
-  if (smem_base != kSmemBase) {  // the fixed-address table needs the documented layout
+  if (smem_base != kSmemBase) {  // the fixed-address tables need the documented layout
     if (threadIdx.x == 0) atomicExch(&g_decode_status, 3);
     return;
   }
@@ -258,19 +266,20 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
   __syncthreads();
 
   // ---- this warp's loader: lane c issues chunk c of a tile --------------------------------
-  // chunks: 0 K codes (1024 B), 1 K statistics (256), 2/3 V codes of tokens 0-7 / 8-15 (512 each),
-  // then V statistics: one 256 B chunk for 16-token pages, else one 64 B chunk per group.
+  // chunks: 0/1 K codes of tokens 0-7 / 8-15 (512 B each), 2 K statistics (256), 3/4 V codes
+  // (512 each), then V statistics: one 256 B chunk for 16-token pages, else 64 B per group.
   const PageGeom geo = make_geom(BS, p.heads_kv);
-  const int n_chunks = tiles_per_page == 1 ? 5 : 8;
+  const int n_chunks = tiles_per_page == 1 ? 6 : 9;
   uint32_t ch_src = 0, ch_sub = 0, ch_dst = 0, ch_bytes = 0;
   {
     const uint32_t code_head = head * (BS * kWordsPerHead) * 4;
-    if (lane == 0) { ch_src = geo.k_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffKCode; ch_bytes = 1024; }
-    if (lane == 1) { ch_src = (geo.k_stat_off + head * (BS * 4)) * 4; ch_sub = 256; ch_dst = kOffKStat; ch_bytes = 256; }
-    if (lane == 2) { ch_src = geo.v_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffVCode; ch_bytes = 512; }
-    if (lane == 3) { ch_src = geo.v_code_off * 4 + code_head + 512; ch_sub = 1024; ch_dst = kOffVCode + 512 + kVCodeSkew; ch_bytes = 512; }
-    if (lane >= 4 && lane < n_chunks) {
-      const int gg = lane - 4;
+    if (lane == 0) { ch_src = geo.k_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffKLo; ch_bytes = 512; }
+    if (lane == 1) { ch_src = geo.k_code_off * 4 + code_head + 512; ch_sub = 1024; ch_dst = kOffKHi; ch_bytes = 512; }
+    if (lane == 2) { ch_src = (geo.k_stat_off + head * (BS * 4)) * 4; ch_sub = 256; ch_dst = kOffKStat; ch_bytes = 256; }
+    if (lane == 3) { ch_src = geo.v_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffVLo; ch_bytes = 512; }
+    if (lane == 4) { ch_src = geo.v_code_off * 4 + code_head + 512; ch_sub = 1024; ch_dst = kOffVHi; ch_bytes = 512; }
+    if (lane >= 5 && lane < n_chunks) {
+      const int gg = lane - 5;
       ch_src = (geo.v_stat_off + head * (4 * BS) + gg * BS) * 4;
       ch_sub = 64;
       ch_dst = kOffVStat + gg * 64;
@@ -304,10 +313,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
     if (lane < n_chunks && !(nocopy && ki >= STAGES))
       bulk_copy_g2s(slot_addr(slot) + ch_dst, src_base + phys * page_bytes + sub * ch_sub, ch_bytes, full);
   };
-  {
-    const int first = noload ? min(my_tiles, STAGES) : min(my_tiles, STAGES);
-    for (int ki = 0; ki < first; ++ki) issue_tile(ki);
-  }
+  for (int ki = 0; ki < min(my_tiles, STAGES); ++ki) issue_tile(ki);
 
   {  // level tables -> fp16 in shared memory
     __half* lv = reinterpret_cast<__half*>(gptr(L::kLevels));
@@ -317,86 +323,104 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
     }
   }
   __syncthreads();
-  {  // byte -> (level[low nibble], level[high nibble]) table, one copy per bank
+  {  // byte -> (level[low nibble], level[high nibble]) tables, one copy per bank.
+     // Block P (P = 0, 1) holds, in bank l, the K table of group 2*((l>>1)&1)+P and the
+     // V table of group 2*(l>>4)+P: the groups lane l needs when an MMA works on pair P.
     const unsigned short* lv = reinterpret_cast<const unsigned short*>(gptr(L::kLevels));
-    const int kg = lane & 3, vg = lane >> 3;
-    for (int e = warp; e < 256; e += NW) {
-      const uint32_t kval = lv[kg * 16 + (e & 15)] | (static_cast<uint32_t>(lv[kg * 16 + (e >> 4)]) << 16);
-      const uint32_t vval = lv[64 + vg * 16 + (e & 15)] | (static_cast<uint32_t>(lv[64 + vg * 16 + (e >> 4)]) << 16);
-      uint32_t* row = reinterpret_cast<uint32_t*>(gptr(kLutAddr + e * 256));
+    for (int e = warp; e < 512; e += NW) {
+      const int P = e >> 8, byte = e & 255;
+      const int kg = 2 * ((lane >> 1) & 1) + P, vg = 2 * (lane >> 4) + P;
+      const uint32_t kval = lv[kg * 16 + (byte & 15)] | (static_cast<uint32_t>(lv[kg * 16 + (byte >> 4)]) << 16);
+      const uint32_t vval = lv[64 + vg * 16 + (byte & 15)] | (static_cast<uint32_t>(lv[64 + vg * 16 + (byte >> 4)]) << 16);
+      uint32_t* row = reinterpret_cast<uint32_t*>(gptr(kLutAddr + P * kLutBlock + byte * 256));
       row[lane] = kval;
       row[32 + lane] = vval;
     }
   }
 
-  // ---- query fragments (A operand of QK), pre-scaled by softmax_scale * log2(e) --------
-  const int hsel = gid & 3;         // query head of this lane's scores / B columns
-  const int grow = 2 * (gid >> 2);  // K group of MMA row gid (row gid+8 is group grow+1)
-  uint32_t qa[8][4];
-  float qs0, qs1;
-  {
-    const bool live = hsel < nh;
-    const int64_t qoff = static_cast<int64_t>(b) * p.q_batch_stride + static_cast<int64_t>(hq0 + hsel) * kHeadDim;
-    const bool m0 = tig == grow, m1 = tig == grow + 1;
-    float qsum = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float f[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) f[i] = live ? load_q(p.q, qoff + 32 * tig + 4 * j + i, p.q_dtype) * p.scale_log2 : 0.f;
-      const uint32_t lo2 = pack_half2(f[0], f[1]), hi2 = pack_half2(f[2], f[3]);
-      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo2));
-      const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&hi2));
-      qsum += (a.x + a.y) + (c.x + c.y);
-      qa[j][0] = m0 ? lo2 : 0u;
-      qa[j][1] = m1 ? lo2 : 0u;
-      qa[j][2] = m0 ? hi2 : 0u;
-      qa[j][3] = m1 ? hi2 : 0u;
-    }
-    qs0 = __shfl_sync(0xffffffffu, qsum, gid * 4 + grow);
-    qs1 = __shfl_sync(0xffffffffu, qsum, gid * 4 + grow + 1);
-  }
-  __syncthreads();  // table complete
-
-  // ---- per-lane constants ---------------------------------------------------------------
-  const int gv = gid >> 1, vu = gid & 1;  // V group / nibble parity of this lane's MMA rows
-  const uint32_t klane = kLutAddr | (lane * 4), vlane = kLutAddr | (lane * 4 + 128);
-  // token whose K codes this lane feeds into column gid of the two QK halves
-  const int kprov0 = (kTok0 >> (4 * gid)) & 15, kprov1 = (kTok1 >> (4 * gid)) & 15;
-  const uint32_t kc_off0 = kOffKCode + kprov0 * 64 + tig * 16, kc_off1 = kOffKCode + kprov1 * 64 + tig * 16;
-  // tokens of this lane's columns / k-slots 2tig, 2tig+1 in the two halves
+  // ---- per-lane roles ---------------------------------------------------------------------
+  // QK (S[token, (head, group)] = Lk[token, d] * Qblock[d, (head, group)], pair P at a time):
+  //   A rows gid / gid+8 are tokens tq0 / tq1; this lane's k-slots carry half `khalf` of group 2*ksel+P.
+  //   B column gid is (head gid&3, group 2*(gid>>2)+P); C columns 2tig, 2tig+1 are heads hA, hA+1 of group 2*ksel+P.
+  const int ksel = tig >> 1, khalf = tig & 1;
+  const int hA = (2 * tig) & 3;
+  const int prow = (kRowSlot >> (4 * gid)) & 15;  // k-slot of the PV stage that A row gid corresponds to
+  const int tq0 = static_cast<int>((kTokOfSlot >> (4 * prow)) & 15), tq1 = static_cast<int>((kTokOfSlot >> (4 * (prow + 8))) & 15);
+  auto code_off = [](int t) { return t * 64 + (t >= 8 ? kCodeSkew : 0); };
+  const uint32_t kc_off0 = kOffKLo + code_off(tq0) + (2 * ksel) * 16 + khalf * 8;  // pair 1: +16
+  const uint32_t kc_off1 = kOffKLo + code_off(tq1) + (2 * ksel) * 16 + khalf * 8;
+  const uint32_t ks_off0 = kOffKStat + tq0 * 16 + ksel * 8, ks_off1 = kOffKStat + tq1 * 16 + ksel * 8;
+  // PV (O[d, (head, group)] = Lv^T[d, token] * W[token, (head, group)], pair P at a time):
+  //   A rows gid / gid+8 are d's of group 2*vsel+P; k-slots 2tig, 2tig+1 (+8) are tokens tk[o][0..1];
+  //   B column gid is (head gid&3, group 2*vsel+P).
+  const int vsel = gid >> 2, vu = gid & 3;
   int tk[2][2];
-  tk[0][0] = (kTok0 >> (8 * tig)) & 15;
-  tk[0][1] = (kTok0 >> (8 * tig + 4)) & 15;
-  tk[1][0] = (kTok1 >> (8 * tig)) & 15;
-  tk[1][1] = (kTok1 >> (8 * tig + 4)) & 15;
-  uint32_t ks_off[2][2], vc_off[2][2], vs_off[2];
+#pragma unroll
+  for (int o = 0; o < 2; ++o)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) tk[o][e] = static_cast<int>((kTokOfSlot >> (4 * (2 * tig + e + 8 * o))) & 15);
+  uint32_t vc_off[2][2], vs_off[2];
 #pragma unroll
   for (int o = 0; o < 2; ++o) {
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      ks_off[o][e] = kOffKStat + tk[o][e] * 16 + grow * 4;
-      vc_off[o][e] = kOffVCode + tk[o][e] * 64 + (tk[o][e] >= 8 ? kVCodeSkew : 0) + gv * 16;
-    }
-    vs_off[o] = kOffVStat + ((gid >> 2) * kTile + min(tk[o][0], tk[o][1])) * 4;
+    for (int e = 0; e < 2; ++e) vc_off[o][e] = kOffVLo + code_off(tk[o][e]) + (2 * vsel) * 16 + (vu >> 1) * 8;  // pair 1: +16
+    vs_off[o] = kOffVStat + ((2 * vsel) * kTile + min(tk[o][0], tk[o][1])) * 4;                                  // pair 1: +64
   }
   const bool pair_swapped = tk[0][0] > tk[0][1];  // odd tig: the pair sits in memory as (second, first)
   const uint32_t sel_scale = pair_swapped ? 0x1054u : 0x5410u, sel_min = pair_swapped ? 0x3276u : 0x7632u;
-  const int sh0 = 4 * vu, sh1 = 4 - 4 * vu;
+  const int sh0 = 4 * (vu & 1), sh1 = 4 - sh0;
+  const uint32_t klane0 = kLutAddr | (lane * 4), klane1 = klane0 + kLutBlock;
+  const uint32_t vlane0 = kLutAddr | (lane * 4 + 128), vlane1 = vlane0 + kLutBlock;
+  // probabilities travel from the QK layout (token by gid, head by tig) to the PV layout (token by tig, head by gid)
+  const int hsrc = gid & 3;  // head of this lane's W column
+  const int src_tig = (hsrc >> 1) | ((hsrc & 1) << 1);
+  const int src_lane0 = ((kRowSlot >> (4 * (2 * tig))) & 15) * 4 + src_tig;      // row holding k-slots 2tig, 2tig+8
+  const int src_lane1 = ((kRowSlot >> (4 * (2 * tig + 1))) & 15) * 4 + src_tig;  // row holding k-slots 2tig+1, 2tig+9
 
-  float oacc[8][2][4];
+  // ---- query fragments (B operand of QK), pre-scaled by softmax_scale * log2(e) ------------
+  uint32_t qb[2][4][2];
+  float qs[2][2];  // sum over d of the rounded q for (head hA+e, group 2*ksel+P)
+  {
+    const int hq = gid & 3;
+    const bool live = hq < nh && ksel == (gid >> 2);
+    const int64_t qoff = static_cast<int64_t>(b) * p.q_batch_stride + static_cast<int64_t>(hq0 + hq) * kHeadDim;
+    float part[2] = {0.f, 0.f};
+#pragma unroll
+    for (int P = 0; P < 2; ++P)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int d0 = 32 * (2 * ksel + P) + 16 * khalf + 4 * j;
+        float f[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = live ? load_q(p.q, qoff + d0 + i, p.q_dtype) * p.scale_log2 : 0.f;
+        const uint32_t lo2 = pack_half2(f[0], f[1]), hi2 = pack_half2(f[2], f[3]);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo2));
+        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&hi2));
+        part[P] += (a.x + a.y) + (c.x + c.y);
+        qb[P][j][0] = lo2;
+        qb[P][j][1] = hi2;
+      }
+#pragma unroll
+    for (int P = 0; P < 2; ++P) {
+      part[P] += __shfl_xor_sync(0xffffffffu, part[P], 1);  // both halves of the group
+#pragma unroll
+      for (int e = 0; e < 2; ++e) qs[e][P] = __shfl_sync(0xffffffffu, part[P], (ksel * 4 + hA + e) * 4 + tig);
+    }
+  }
+  __syncthreads();  // tables complete
+
+  float oacc[2][4][4];
   float cmin[2][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int P = 0; P < 2; ++P) {
 #pragma unroll
-    for (int jn = 0; jn < 2; ++jn)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) oacc[i][jn][c] = 0.f;
+      for (int c = 0; c < 4; ++c) oacc[P][i][c] = 0.f;
 #pragma unroll
-  for (int jn = 0; jn < 2; ++jn)
-#pragma unroll
-    for (int c = 0; c < 4; ++c) cmin[jn][c] = 0.f;
-  float m_used = -CUDART_INF_F, l_run = 0.f;
+    for (int c = 0; c < 4; ++c) cmin[P][c] = 0.f;
+  }
+  float m_used[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};  // heads hA, hA+1
 
   // ---- main loop: two ring tiles (32 tokens) per iteration -------------------------------
   auto wait_tile = [&](int k) -> bool {  // false: the bounded wait gave up
@@ -420,128 +444,138 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
   };
 
   // timing ablations (ABL): bit 0 drops the MMAs, bit 1 replaces table look-ups by their address
-#define BKV_MMA(c, a0, a1, a2, a3, b0, b1) \
-  do { if (ABL & 1) { asm volatile("" ::"r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1)); } else { mma16816(c, a0, a1, a2, a3, b0, b1); } } while (0)
+#define BKV_MMA(c, a0, a1, a2, a3, b0, b1)                                                      \
+  do {                                                                                          \
+    if (ABL & 1) {                                                                              \
+      asm volatile("" ::"r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));                  \
+    } else {                                                                                    \
+      mma16816(c, a0, a1, a2, a3, b0, b1);                                                      \
+    }                                                                                           \
+  } while (0)
 #define BKV_LUT(a) ((ABL & 2) ? (a) : lut_load(a))
   auto process_pair = [&](auto partial_tag, const uint32_t sbA, const uint32_t sbB, const int nvA, const int nvB) {
     constexpr bool PARTIAL = decltype(partial_tag)::value;
     const uint32_t sb[2] = {sbA, sbB};
     const int nv[2] = {nvA, nvB};
-    // ------------------------------ S^T = Q * Lk^T (4 independent accumulator chains) ------
+    // ------------------------------ S = Lk * Qblock (one accumulator per tile and pair) ------
     float sacc[2][2][4] = {};
 #pragma unroll
     for (int t = 0; t < 2; ++t)
 #pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const uint4 kw = ring_load128(sb[t] + (o ? kc_off1 : kc_off0));
-        const uint32_t w4[4] = {kw.x, kw.y, kw.z, kw.w};
-        // all 16 look-up addresses first, then the 16 look-ups, then the 8 dependent MMAs
-        uint32_t ad[8][2], bv[8][2];
+      for (int P = 0; P < 2; ++P) {
+        const uint2 k0 = P ? ring_load64<16>(sb[t] + kc_off0) : ring_load64<0>(sb[t] + kc_off0);
+        const uint2 k1 = P ? ring_load64<16>(sb[t] + kc_off1) : ring_load64<0>(sb[t] + kc_off1);
+        const uint32_t w0[2] = {k0.x, k0.y}, w1[2] = {k1.x, k1.y};
+        const uint32_t kl = P ? klane1 : klane0;
+        uint32_t av[4][4];
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          ad[jj][0] = __byte_perm(w4[jj >> 1], klane, (jj & 1) ? 0x7624 : 0x7604);
-          ad[jj][1] = __byte_perm(w4[jj >> 1], klane, (jj & 1) ? 0x7634 : 0x7614);
+        for (int j = 0; j < 4; ++j) {
+          av[j][0] = BKV_LUT(__byte_perm(w0[j >> 1], kl, (j & 1) ? 0x7624 : 0x7604));
+          av[j][1] = BKV_LUT(__byte_perm(w1[j >> 1], kl, (j & 1) ? 0x7624 : 0x7604));
+          av[j][2] = BKV_LUT(__byte_perm(w0[j >> 1], kl, (j & 1) ? 0x7634 : 0x7614));
+          av[j][3] = BKV_LUT(__byte_perm(w1[j >> 1], kl, (j & 1) ? 0x7634 : 0x7614));
         }
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          bv[jj][0] = BKV_LUT(ad[jj][0]);
-          bv[jj][1] = BKV_LUT(ad[jj][1]);
-        }
-#pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
-          if (jj == 0 && !(ABL & 1)) mma16816_zero(sacc[t][o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], bv[jj][0], bv[jj][1]);
-          else BKV_MMA(sacc[t][o], qa[jj][0], qa[jj][1], qa[jj][2], qa[jj][3], bv[jj][0], bv[jj][1]);
-        }
+        for (int j = 0; j < 4; ++j)
+          BKV_MMA(sacc[t][P], av[j][0], av[j][1], av[j][2], av[j][3], qb[P][j][0], qb[P][j][1]);
       }
     // ------------------------------ V index bytes (token pair -> one table index) -----------
     // Independent of the softmax below, so issued here to overlap with its latency.
-    uint32_t vidx[2][2][4];
+    uint32_t vidx[2][2][2][2];  // [tile][pair][token pair][word: row gid / row gid+8]
 #pragma unroll
     for (int t = 0; t < 2; ++t)
 #pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const uint4 xf = ring_load128(sb[t] + vc_off[o][0]);
-        const uint4 xs = ring_load128(sb[t] + vc_off[o][1]);
-        vidx[t][o][0] = ((xf.x >> sh0) & 0x0F0F0F0Fu) | ((xs.x << sh1) & 0xF0F0F0F0u);
-        vidx[t][o][1] = ((xf.y >> sh0) & 0x0F0F0F0Fu) | ((xs.y << sh1) & 0xF0F0F0F0u);
-        vidx[t][o][2] = ((xf.z >> sh0) & 0x0F0F0F0Fu) | ((xs.z << sh1) & 0xF0F0F0F0u);
-        vidx[t][o][3] = ((xf.w >> sh0) & 0x0F0F0F0Fu) | ((xs.w << sh1) & 0xF0F0F0F0u);
-      }
-    // ------------------------------ scores of this lane -------------------------------------
-    float s[2][2][2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t)
-#pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const uint2 st0 = ring_load64<0>(sb[t] + ks_off[o][0]);
-        const uint2 st1 = ring_load64<0>(sb[t] + ks_off[o][1]);
-        const float2 a0 = stat_word_to_f32<STAT_BF16>(st0.x), b0 = stat_word_to_f32<STAT_BF16>(st0.y);
-        const float2 a1 = stat_word_to_f32<STAT_BF16>(st1.x), b1 = stat_word_to_f32<STAT_BF16>(st1.y);
-        float p0 = a0.x * sacc[t][o][0];
-        p0 = fmaf(a0.y, qs0, p0);
-        p0 = fmaf(b0.x, sacc[t][o][2], p0);
-        p0 = fmaf(b0.y, qs1, p0);
-        float p1 = a1.x * sacc[t][o][1];
-        p1 = fmaf(a1.y, qs0, p1);
-        p1 = fmaf(b1.x, sacc[t][o][3], p1);
-        p1 = fmaf(b1.y, qs1, p1);
-        p0 += __shfl_xor_sync(0xffffffffu, p0, 16);
-        p1 += __shfl_xor_sync(0xffffffffu, p1, 16);
-        if (PARTIAL) {  // tokens behind the end of the sequence (their statistics may be NaN)
-          if (tk[o][0] >= nv[t]) p0 = -CUDART_INF_F;
-          if (tk[o][1] >= nv[t]) p1 = -CUDART_INF_F;
-        }
-        s[t][o][0] = p0;
-        s[t][o][1] = p1;
-      }
-    // ------------------------------ online softmax over the 32 tokens -----------------------
-    float tmax = fmaxf(fmaxf(fmaxf(s[0][0][0], s[0][0][1]), fmaxf(s[0][1][0], s[0][1][1])),
-                       fmaxf(fmaxf(s[1][0][0], s[1][0][1]), fmaxf(s[1][1][0], s[1][1][1])));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-    const bool need = tmax > m_used + kRescaleThreshold;
-    if (__any_sync(0xffffffffu, need)) {
-      const float m_new = need ? tmax : m_used;
-      const float corr = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_used - m_new);
-      m_used = m_new;
-      l_run *= corr;
-      const float ce = __shfl_sync(0xffffffffu, corr, ((2 * tig) & 3) * 4);
-      const float co = __shfl_sync(0xffffffffu, corr, ((2 * tig + 1) & 3) * 4);
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int jn = 0; jn < 2; ++jn) {
-          oacc[i][jn][0] *= ce;
-          oacc[i][jn][1] *= co;
-          oacc[i][jn][2] *= ce;
-          oacc[i][jn][3] *= co;
-        }
-#pragma unroll
-      for (int jn = 0; jn < 2; ++jn) {
-        cmin[jn][0] *= ce;
-        cmin[jn][1] *= co;
-        cmin[jn][2] *= ce;
-        cmin[jn][3] *= co;
-      }
-    }
-    uint32_t ph[2][2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t)
-#pragma unroll
-      for (int o = 0; o < 2; ++o) {
-        const float e0 = fast_exp2(s[t][o][0] - m_used), e1 = fast_exp2(s[t][o][1] - m_used);
-        l_run += e0 + e1;
-        ph[t][o] = pack_half2(e0, e1);
-      }
-    // ------------------------------ per tile: W = p*scale_v, p*min_v, then O += Lv^T * W ----
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      uint32_t wb[2][2], mb[2][2];
-#pragma unroll
-      for (int jn = 0; jn < 2; ++jn)
+      for (int P = 0; P < 2; ++P)
 #pragma unroll
         for (int o = 0; o < 2; ++o) {
-          const uint2 vs = jn ? ring_load64<2 * kTile * 4>(sb[t] + vs_off[o]) : ring_load64<0>(sb[t] + vs_off[o]);
+          const uint2 xf = P ? ring_load64<16>(sb[t] + vc_off[o][0]) : ring_load64<0>(sb[t] + vc_off[o][0]);
+          const uint2 xs = P ? ring_load64<16>(sb[t] + vc_off[o][1]) : ring_load64<0>(sb[t] + vc_off[o][1]);
+          vidx[t][P][o][0] = ((xf.x >> sh0) & 0x0F0F0F0Fu) | ((xs.x << sh1) & 0xF0F0F0F0u);
+          vidx[t][P][o][1] = ((xf.y >> sh0) & 0x0F0F0F0Fu) | ((xs.y << sh1) & 0xF0F0F0F0u);
+        }
+    // ------------------------------ scores: tokens tq0, tq1 x heads hA, hA+1 ----------------
+    float s[2][2][2];  // [tile][row][head]
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const uint2 st = ring_load64<0>(sb[t] + (r ? ks_off1 : ks_off0));  // groups 2*ksel, 2*ksel+1
+        const float2 g0 = stat_word_to_f32<STAT_BF16>(st.x), g1 = stat_word_to_f32<STAT_BF16>(st.y);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float v = g0.x * sacc[t][0][2 * r + e];
+          v = fmaf(g0.y, qs[e][0], v);
+          v = fmaf(g1.x, sacc[t][1][2 * r + e], v);
+          v = fmaf(g1.y, qs[e][1], v);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);  // the other two groups
+          if (PARTIAL) {                            // behind the end of the sequence (statistics may be NaN)
+            if ((r ? tq1 : tq0) >= nv[t]) v = -CUDART_INF_F;
+          }
+          s[t][r][e] = v;
+        }
+      }
+    // ------------------------------ online softmax over the 32 tokens -----------------------
+    float tmax[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float m = fmaxf(fmaxf(s[0][0][e], s[0][1][e]), fmaxf(s[1][0][e], s[1][1][e]));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+      tmax[e] = m;
+    }
+    const bool need0 = tmax[0] > m_used[0] + kRescaleThreshold, need1 = tmax[1] > m_used[1] + kRescaleThreshold;
+    if (__any_sync(0xffffffffu, need0 || need1)) {
+      float corr[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float m_new = (e ? need1 : need0) ? tmax[e] : m_used[e];
+        corr[e] = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_used[e] - m_new);
+        m_used[e] = m_new;
+        l_run[e] *= corr[e];
+      }
+#pragma unroll
+      for (int P = 0; P < 2; ++P) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          oacc[P][i][0] *= corr[0];
+          oacc[P][i][1] *= corr[1];
+          oacc[P][i][2] *= corr[0];
+          oacc[P][i][3] *= corr[1];
+        }
+        cmin[P][0] *= corr[0];
+        cmin[P][1] *= corr[1];
+        cmin[P][2] *= corr[0];
+        cmin[P][3] *= corr[1];
+      }
+    }
+    uint32_t ph[2][2];  // [tile][token pair]: probabilities of this lane's W column head, tokens tk[o][0..1]
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      float pe[2][2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          pe[r][e] = fast_exp2(s[t][r][e] - m_used[e]);
+          l_run[e] += pe[r][e];
+        }
+      // this lane serves head hA + ksel to the PV layout: (token tq0, token tq1) packed
+      const uint32_t mine = ksel ? pack_half2(pe[0][1], pe[1][1]) : pack_half2(pe[0][0], pe[1][0]);
+      const uint32_t fromA = __shfl_sync(0xffffffffu, mine, src_lane0);  // tokens of k-slots 2tig, 2tig+8
+      const uint32_t fromB = __shfl_sync(0xffffffffu, mine, src_lane1);  // tokens of k-slots 2tig+1, 2tig+9
+      ph[t][0] = __byte_perm(fromA, fromB, 0x5410);
+      ph[t][1] = __byte_perm(fromA, fromB, 0x7632);
+    }
+    // ------------------------------ per tile: W = p*scale_v, p*min_v, then O += Lv^T * W ----
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int P = 0; P < 2; ++P) {
+        uint32_t wb[2], mb[2];
+#pragma unroll
+        for (int o = 0; o < 2; ++o) {
+          const uint2 vs = P ? ring_load64<kTile * 4>(sb[t] + vs_off[o]) : ring_load64<0>(sb[t] + vs_off[o]);
           uint32_t sc2, mn2;
           if (STAT_BF16) {
             const uint32_t first = pair_swapped ? vs.y : vs.x, second = pair_swapped ? vs.x : vs.y;
@@ -557,39 +591,24 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
             wv &= keep;
             mv &= keep;
           }
-          wb[jn][o] = wv;
-          mb[jn][o] = mv;
+          wb[o] = wv;
+          mb[o] = mv;
+        }
+        const uint32_t vl = P ? vlane1 : vlane0;
+        uint32_t av[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t sel = i == 0 ? 0x7604 : i == 1 ? 0x7614 : i == 2 ? 0x7624 : 0x7634;
+          av[i][0] = BKV_LUT(__byte_perm(vidx[t][P][0][0], vl, sel));
+          av[i][1] = BKV_LUT(__byte_perm(vidx[t][P][0][1], vl, sel));
+          av[i][2] = BKV_LUT(__byte_perm(vidx[t][P][1][0], vl, sel));
+          av[i][3] = BKV_LUT(__byte_perm(vidx[t][P][1][1], vl, sel));
         }
 #pragma unroll
-      for (int wi = 0; wi < 4; ++wi) {
-        const uint32_t m0 = vidx[t][0][wi], m1 = vidx[t][1][wi];
-        uint32_t aa[8], av[2][4];
-        aa[0] = __byte_perm(m0, vlane, 0x7604);
-        aa[1] = __byte_perm(m0, vlane, 0x7614);
-        aa[2] = __byte_perm(m0, vlane, 0x7624);
-        aa[3] = __byte_perm(m0, vlane, 0x7634);
-        aa[4] = __byte_perm(m1, vlane, 0x7604);
-        aa[5] = __byte_perm(m1, vlane, 0x7614);
-        aa[6] = __byte_perm(m1, vlane, 0x7624);
-        aa[7] = __byte_perm(m1, vlane, 0x7634);
-        av[0][0] = BKV_LUT(aa[0]);
-        av[0][1] = BKV_LUT(aa[1]);
-        av[1][0] = BKV_LUT(aa[2]);
-        av[1][1] = BKV_LUT(aa[3]);
-        av[0][2] = BKV_LUT(aa[4]);
-        av[0][3] = BKV_LUT(aa[5]);
-        av[1][2] = BKV_LUT(aa[6]);
-        av[1][3] = BKV_LUT(aa[7]);
-#pragma unroll
-        for (int e = 0; e < 2; ++e)
-#pragma unroll
-          for (int jn = 0; jn < 2; ++jn)
-            BKV_MMA(oacc[2 * wi + e][jn], av[e][0], av[e][1], av[e][2], av[e][3], wb[jn][0], wb[jn][1]);
+        for (int i = 0; i < 4; ++i) BKV_MMA(oacc[P][i], av[i][0], av[i][1], av[i][2], av[i][3], wb[0], wb[1]);
+        const uint32_t ones = 0x3C003C00u;
+        BKV_MMA(cmin[P], ones, ones, ones, ones, mb[0], mb[1]);
       }
-      const uint32_t ones = 0x3C003C00u;
-#pragma unroll
-      for (int jn = 0; jn < 2; ++jn) BKV_MMA(cmin[jn], ones, ones, ones, ones, mb[jn][0], mb[jn][1]);
-    }
   };
 
   for (int k = 0; k < my_tiles; k += 2) {
@@ -609,33 +628,39 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_mma_kernel(const DecodePara
       if (k + 1 + STAGES < my_tiles) issue_tile(k + 1 + STAGES);
     }
   }
+#undef BKV_MMA
+#undef BKV_LUT
 
   // ---- epilogue: warp partials -> shared memory -> CTA result ---------------------------
-  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {  // tokens were spread over gid
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 4);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 8);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 16);
+  }
   __syncthreads();  // every tile of every warp has been consumed: the ring is free
   float* mo = reinterpret_cast<float*>(gptr(L::kMergeO));
   float* mm = reinterpret_cast<float*>(gptr(L::kMergeM));
   float* ml = reinterpret_cast<float*>(gptr(L::kMergeL));
-  if ((tig >> 1) == (gv & 1)) {
-    const bool hi_tile = (gv >> 1) != 0;
-    const int h0 = (2 * tig) & 3;
-    const float c0 = hi_tile ? cmin[1][0] : cmin[0][0];
-    const float c1 = hi_tile ? cmin[1][1] : cmin[0][1];
-    float* base0 = mo + (warp * 4 + h0) * kHeadDim;
+  if (ksel == vsel) {  // accumulator columns of this lane match the group of its rows
+    float* base0 = mo + (warp * 4 + hA) * kHeadDim;
     float* base1 = base0 + kHeadDim;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int d0 = 32 * gv + 4 * i + vu;
-      base0[d0] = (hi_tile ? oacc[i][1][0] : oacc[i][0][0]) + c0;
-      base1[d0] = (hi_tile ? oacc[i][1][1] : oacc[i][0][1]) + c1;
-      base0[d0 + 2] = (hi_tile ? oacc[i][1][2] : oacc[i][0][2]) + c0;
-      base1[d0 + 2] = (hi_tile ? oacc[i][1][3] : oacc[i][0][3]) + c1;
-    }
+    for (int P = 0; P < 2; ++P)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int d0 = 32 * (2 * vsel + P) + 16 * (vu >> 1) + 2 * i + (vu & 1);
+        base0[d0] = oacc[P][i][0] + cmin[P][0];
+        base1[d0] = oacc[P][i][1] + cmin[P][1];
+        base0[d0 + 8] = oacc[P][i][2] + cmin[P][0];
+        base1[d0 + 8] = oacc[P][i][3] + cmin[P][1];
+      }
   }
-  if (tig == 0 && gid < 4) {
-    mm[warp * 4 + gid] = m_used;
-    ml[warp * 4 + gid] = l_run;
+  if (gid == 0 && ksel == 0) {  // tig 0 holds heads 0,1; tig 1 holds heads 2,3
+    mm[warp * 4 + hA] = m_used[0];
+    mm[warp * 4 + hA + 1] = m_used[1];
+    ml[warp * 4 + hA] = l_run[0];
+    ml[warp * 4 + hA + 1] = l_run[1];
   }
   __syncthreads();
   const bool direct = S == 1 && !p.force_partial;
@@ -705,14 +730,12 @@ int launch_decode_mma(const DecodeParams& p, cudaStream_t stream, int config) {
   if (p.token_lo % p.block_size != 0) return BKV_ERR_UNSUPPORTED;
   switch (config) {
     case 1: return launch_variant<8, 4>(p, stream);
-    case 2: return launch_variant<8, 6>(p, stream);
-    case 3: return launch_variant<12, 5>(p, stream);
-    case 4: return launch_variant<16, 3>(p, stream);
-    case 5: return launch_variant<12, 4>(p, stream);
-    case 10: return launch_variant<8, 4, 1>(p, stream);
-    case 11: return launch_variant<8, 4, 2>(p, stream);
-    case 12: return launch_variant<8, 4, 3>(p, stream);
-    default: return launch_variant<8, 4>(p, stream);
+    case 2: return launch_variant<12, 3>(p, stream);
+    case 3: return launch_variant<16, 2>(p, stream);
+    case 4: return launch_variant<9, 4>(p, stream);
+    case 10: return launch_variant<12, 3, 1>(p, stream);
+    case 11: return launch_variant<12, 3, 2>(p, stream);
+    default: return launch_variant<12, 3>(p, stream);
   }
 }
 
