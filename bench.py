@@ -53,7 +53,9 @@ def parse_args():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0, help="0 = launch policy")
     ap.add_argument("--stat", default="fp16", choices=["fp16", "bf16"])
-    ap.add_argument("--variant", type=int, default=0, help="0 auto, 1 CUDA-core kernel, 2 tensor-core kernel")
+    ap.add_argument("--variant", type=int, default=0,
+                    help="0 auto (persistent tensor-core schedule), 1 CUDA-core kernel, 20+ split-grid tensor-core "
+                         "configurations, 40+ persistent configurations")
     ap.add_argument("--cpu-sample-requests", type=int, default=0, help="0 = one per host core")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dense-baseline", action="store_true", help="also time the bf16-KV kernel on the same shapes")
@@ -255,6 +257,7 @@ def main():
                                 max_seq_len=max_seq_len, num_splits=args.splits)
     ws = rt.allocate_runtime_workspace(spec, device=dev)
     scale = synth.softmax_scale()
+    streamed = (args.variant == 0 or args.variant >= 40) and "stream" in ws
 
     def decode_step():
         rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=block_table,
@@ -359,7 +362,8 @@ def main():
             "vs_baseline": None,
             "dtype": "f16 tensor-core operands, f32 accumulate" if args.variant != 1 else "f32",
             "data": "synthetic",
-            "config": dict(workload_config(args), num_splits=spec.num_splits, kernel_variant=args.variant),
+            "config": dict(workload_config(args), num_splits=0 if streamed else spec.num_splits,
+                           schedule="persistent" if streamed else "split", kernel_variant=args.variant),
             "roofline": {
                 "bound": "hbm",
                 "achieved": achieved,
@@ -373,7 +377,7 @@ def main():
             },
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * (2 if spec.num_splits > 1 else 1),
+            "gpu_launches": args.steps * (2 if (streamed or spec.num_splits > 1) else 1),
             "clocks": clocks,
         }
         if dense is not None:

@@ -35,6 +35,9 @@ SIGNATURES = {
                          _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
     "bkv_decode_noalloc_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _I, _P,
                                  _I, _I, _I, _I, _F, _I, _P],
+    "bkv_decode_stream_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _I, _P,
+                                _P, _L, _I, _I, _I, _F, _I, _I, _P],
+    "bkv_decode_stream_workspace_bytes": [],
     "bkv_decode_device_status": [_P],
     "bkv_combine_sm100": [_P, _P, _P, _I, _L, _P, _I, _P, _P],
     "bkv_decode_range_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _P,
@@ -75,7 +78,12 @@ def load() -> ctypes.CDLL:
         for name, argtypes in SIGNATURES.items():
             fn = getattr(lib, name)  # AttributeError if the symbol is not exported
             fn.argtypes = argtypes
-            fn.restype = _c.c_char_p if name in ("bkv_status_string", "bkv_last_cuda_error") else _I
+            if name in ("bkv_status_string", "bkv_last_cuda_error"):
+                fn.restype = _c.c_char_p
+            elif name == "bkv_decode_stream_workspace_bytes":
+                fn.restype = _L
+            else:
+                fn.restype = _I
         _lib = lib
         return lib
 

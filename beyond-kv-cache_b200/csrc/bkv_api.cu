@@ -129,9 +129,41 @@ extern "C" int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dty
   return BKV_OK;
 }
 
+extern "C" int64_t bkv_decode_stream_workspace_bytes(void) { return bkv::stream_workspace_bytes(); }
+
+extern "C" int bkv_decode_stream_sm100(const void* q, int64_t q_batch_stride, int q_dtype,
+                                       const void* cache, int64_t num_pages,
+                                       int64_t page_stride_i32, int block_size, int heads_kv,
+                                       int stat_dtype, const int32_t* block_table,
+                                       int64_t block_table_stride, const int32_t* seq_lens,
+                                       const void* lvl_k, const void* lvl_v, int table_dtype,
+                                       void* out, int out_dtype, float* out_f32, void* workspace,
+                                       int64_t workspace_bytes, int batch, int heads_q,
+                                       int max_seq_len, float softmax_scale, int flags,
+                                       int variant, bkv_stream_t stream) {
+  using namespace bkv;
+  DecodeParams p;
+  const int rc = fill_decode_params(p, q, q_batch_stride, q_dtype, cache, num_pages,
+                                    page_stride_i32, block_size, heads_kv, stat_dtype, block_table,
+                                    block_table_stride, seq_lens, lvl_k, lvl_v, table_dtype, batch,
+                                    heads_q, softmax_scale, flags);
+  if (rc != BKV_OK) return rc;
+  if (batch == 0) return BKV_OK;
+  if (!out || !workspace) return BKV_ERR_ARG;
+  if (out_dtype != BKV_F16 && out_dtype != BKV_BF16 && out_dtype != BKV_F32) return BKV_ERR_ARG;
+  if (max_seq_len <= 0) return BKV_ERR_ARG;
+  p.out = out; p.out_dtype = out_dtype; p.out_f32 = out_f32;
+  p.num_splits = 1;
+  p.token_hi = max_seq_len;
+  return launch_decode_stream(p, workspace, workspace_bytes, max_seq_len,
+                              static_cast<cudaStream_t>(stream), variant >= 40 ? variant - 40 : 0);
+}
+
 extern "C" int bkv_decode_device_status(int* status_out) {
   if (!status_out) return BKV_ERR_ARG;
+  const int stream_status = bkv::read_stream_status();
   *status_out = bkv::read_decode_status();
+  if (*status_out == 0) *status_out = stream_status;
   return bkv::check_launch("bkv_decode_device_status");
 }
 

@@ -1,0 +1,805 @@
+// Persistent, warp-granular form of the tensor-core decode attention over the packed cache.
+//
+// The (kv-head, request, 16-token tile) space is one long line, head-major.  The grid is one
+// CTA per SM; CTA c owns the c-th equal share of the line and every warp of it an equal,
+// contiguous share of that.  A warp therefore streams through a run of consecutive tiles that
+// may start in the middle of one request and end in the middle of another; the byte tables are
+// built once per CTA (twice when its share straddles two heads) instead of once per split.
+//
+// A warp keeps a private ring of tiles which it fills itself with bulk copies, running
+// STAGES tiles ahead across request boundaries, and a private online-softmax state; no block
+// barrier is executed while it works.  When it leaves a request it either
+//   * owns the whole request: normalises and writes the attention output, or
+//   * owns a part of it:      writes an un-normalised partial (o, m, l) into one of the two
+//     slots of its range (slot 0: the request began before the range, slot 1: it goes on
+//     behind it) together with a header word naming the request.
+// The fix-up kernel walks the ranges in order, collects the chain of partials of every
+// request that was cut, and merges them by log-sum-exp.
+//
+// Arithmetic and operand layouts (byte tables, group pairs, token permutations) are those of
+// bkv_decode_mma.cu with two changes that remove shuffles and shared-memory traffic:
+//   * MMA column n stands for (query head n/2, group n%2 of the pair), so a lane's two QK
+//     accumulator columns are the two groups of ONE head and its scores need no exchange;
+//   * PV row g / g+8 of MMA i hold the even / odd dimension 8*(g%4)+2i(+1) of a group, so
+//     a lane reads each V code word exactly once and uses both nibbles of every byte.
+#include <math_constants.h>
+
+#include <type_traits>
+
+#include "bkv_decode_common.cuh"
+#include "bkv_mma_ptx.cuh"
+
+namespace bkv {
+
+__device__ int g_stream_status = 0;  // non-zero: 2 a bounded wait gave up, 3 unexpected smem base
+
+namespace {
+
+using namespace mma;
+
+constexpr int kMaxBatch = 1024;
+constexpr int kMaxPagesLog2 = 26;  // a page id and the tile's position in its page share one word
+// ring slot of this kernel: the tile format plus a 16-byte gap in front of the V statistics of
+// groups 2 and 3, which keeps the statistic loads of a half-warp (two groups at once) conflict-free
+constexpr int kVStatSkew = 16;
+constexpr int kSlotBytes = kTileBytes + kVStatSkew;  // 2608
+constexpr uint32_t kRingLoS = kSmemBase + 1920;       // barriers, scan scratch and level tables end at 1536
+constexpr int kLoSlotsS = (kLutAddr - kRingLoS) / kSlotBytes;
+constexpr uint32_t kPrefixAddr = kSmemEnd - 4224;  // int[kMaxBatch + 1] tiles before request b
+constexpr int kHiSlots = (kPrefixAddr - kRingHi) / kSlotBytes;
+constexpr uint32_t kFullBar = kSmemBase;          // 8 B each
+constexpr uint32_t kChunkTot = kSmemBase + 512;   // int[32] scan scratch
+constexpr uint32_t kLevels = kSmemBase + 1280;    // fp16 [K|V][4][16]
+constexpr int kHdrNone = -1;
+
+constexpr int BKV_FLAG_DEBUG_NOLOAD = 0x100;  // timing experiment: reuse the first ring fill
+
+struct StreamParams {
+  DecodeParams d;
+  float* ws_o;   // [slots][4][128]
+  float* ws_m;   // [slots][4]  log2 domain
+  float* ws_l;   // [slots][4]
+  int* ws_hdr;   // [slots]  (virtual head * batch + request) * 2 + (1: last part), or kHdrNone
+  int quads;     // query-head quads per kv head
+};
+
+template <int NW, int STAGES>
+struct Ring {
+  static_assert(NW * STAGES <= 64, "control block holds at most 64 barriers");
+  static constexpr int kWarpsLo = kLoSlotsS / STAGES;
+  static_assert((NW - kWarpsLo) * STAGES <= kHiSlots, "ring does not fit next to the two table blocks");
+  static constexpr int kDynBytes = static_cast<int>(kSmemEnd - kSmemBase);
+  __device__ static uint32_t base(int warp) {
+    return warp < kWarpsLo ? kRingLoS + warp * (STAGES * kSlotBytes)
+                           : kRingHi + (warp - kWarpsLo) * (STAGES * kSlotBytes);
+  }
+};
+
+template <int NW, int STAGES, bool STAT_BF16>
+__global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamParams sp) {
+  using R = Ring<NW, STAGES>;
+  const DecodeParams& p = sp.d;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  if (smem_u32(smem) != kSmemBase) {  // the fixed-address tables need the documented layout
+    if (threadIdx.x == 0) atomicExch(&g_stream_status, 3);
+    return;
+  }
+  auto gptr = [&](uint32_t shared_addr) { return smem + (shared_addr - kSmemBase); };
+  constexpr uint32_t kFull = 0xffffffffu;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int C = gridDim.x, cta = blockIdx.x;
+  const int B = p.batch;
+  const int quads = sp.quads;
+  const int gqa = p.heads_q / p.heads_kv;
+  const int BS = p.block_size;
+  const int log2r = 31 - __clz(BS / kTile);  // tiles per page is a power of two
+  const int tiles_per_page = 1 << log2r;
+  const int lo = max(p.token_lo, 0);
+  const int page_lo = lo / BS;
+  const bool noload = (p.flags & BKV_FLAG_DEBUG_NOLOAD) != 0;
+
+  if (p.flags & BKV_FLAG_PDL_WAIT) pdl_wait();
+
+  if (tid == 0) {
+    for (int i = 0; i < NW * STAGES; ++i) mbar_init(kFullBar + 8 * i, 1);
+    fence_barrier_init();
+  }
+
+  // ---- tiles before every request (exclusive prefix sum over the batch) ------------------
+  int* prefix = reinterpret_cast<int*>(gptr(kPrefixAddr));
+  {
+    int* tot = reinterpret_cast<int*>(gptr(kChunkTot));
+    const int nchunks = (B + 31) >> 5;
+    for (int c = warp; c < nchunks; c += NW) {
+      const int b = 32 * c + lane;
+      int n = 0;
+      if (b < B) {
+        const int hi_b = min(p.token_hi, p.seq_lens[b]);
+        n = hi_b > lo ? (hi_b - lo + kTile - 1) / kTile : 0;
+      }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(kFull, n, o);
+        if (lane >= o) n += y;
+      }
+      if (b < B) prefix[1 + b] = n;
+      if (lane == 31) tot[c] = n;
+    }
+    if (tid == 0) prefix[0] = 0;
+    __syncthreads();
+    if (warp == 0) {
+      const int v = lane < nchunks ? tot[lane] : 0;
+      int n = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(kFull, n, o);
+        if (lane >= o) n += y;
+      }
+      tot[lane] = n - v;
+    }
+    __syncthreads();
+    for (int b = tid; b < B; b += NW * 32) prefix[1 + b] += tot[b >> 5];
+    __syncthreads();
+  }
+  const int Tb = prefix[B];  // tiles of one head
+  // requests without any position to attend are nobody's tiles: their output rows are zeros
+  for (int b = cta; b < B; b += C) {
+    if (prefix[b + 1] != prefix[b]) continue;
+    const int64_t row0 = static_cast<int64_t>(b) * p.heads_q * kHeadDim;
+    for (int i = tid; i < p.heads_q * kHeadDim; i += NW * 32) {
+      store_out(p.out, row0 + i, p.out_dtype, 0.f);
+      if (p.out_f32) p.out_f32[row0 + i] = 0.f;
+    }
+  }
+  const int64_t G = static_cast<int64_t>(p.heads_kv * quads) * Tb;
+  const int64_t ga = G * cta / C, gb = G * (cta + 1) / C;
+
+  // ---- per-lane roles (see the file comment) ----------------------------------------------
+  const int ksel = tig >> 1, khalf = tig & 1;     // QK: this lane's k-slots carry half khalf of group 2*ksel+P
+  const int prow = (kRowSlot >> (4 * gid)) & 15;  // k-slot of the PV stage that QK row gid corresponds to
+  const int tq0 = static_cast<int>((kTokOfSlot >> (4 * prow)) & 15);  // row gid; row gid+8 is token tq0+4
+  const uint32_t kc_off = kOffKLo + code_row_off(tq0) + (2 * ksel) * 16 + khalf * 8;  // +16: pair 1, +256: row gid+8
+  const uint32_t ks_off = kOffKStat + tq0 * 16;                                        // +64: row gid+8
+  const int vsel = gid >> 2, vu = gid & 3;        // PV: rows gid/gid+8 are dims 8*vu+2i(+1) of group 2*vsel+P
+  const int hcol = gid >> 1, gsel = gid & 1;      // B column gid: query head hcol, group 2*gsel+P
+  int tk[2];                                      // tokens of k-slots 2tig, 2tig+1 (slots +8: tokens +4)
+  tk[0] = static_cast<int>((kTokOfSlot >> (4 * (2 * tig))) & 15);
+  tk[1] = static_cast<int>((kTokOfSlot >> (4 * (2 * tig + 1))) & 15);
+  const uint32_t vc_off0 = kOffVLo + code_row_off(tk[0]) + (2 * vsel) * 16 + vu * 4;  // +16: pair 1, +256: slots +8
+  const uint32_t vc_off1 = kOffVLo + code_row_off(tk[1]) + (2 * vsel) * 16 + vu * 4;
+  const uint32_t vs_off = kOffVStat + ((2 * gsel) * kTile + min(tk[0], tk[1])) * 4 + gsel * kVStatSkew;  // +64: pair 1, +16: slots +8
+  const bool pair_swapped = tk[0] > tk[1];  // odd tig: the pair sits in memory as (second, first)
+  const uint32_t sel_scale = pair_swapped ? 0x1054u : 0x5410u, sel_min = pair_swapped ? 0x3276u : 0x7632u;
+  const uint32_t klane0 = kLutAddr | (lane * 4), klane1 = klane0 + kLutBlock;
+  const uint32_t vlane0 = kLutAddr | (lane * 4 + 128), vlane1 = vlane0 + kLutBlock;
+  // probabilities travel from the QK layout (token by gid, head by tig) to the PV layout (token by tig, head by gid)
+  const int src_lane0 = ((kRowSlot >> (4 * (2 * tig))) & 15) * 4 + hcol;      // row holding k-slots 2tig, 2tig+8
+  const int src_lane1 = ((kRowSlot >> (4 * (2 * tig + 1))) & 15) * 4 + hcol;  // row holding k-slots 2tig+1, 2tig+9
+
+  // ---- ring state of this warp: tile number g of its lifetime lives in stage g % STAGES ----
+  const uint32_t ring_base = R::base(warp);
+  const uint32_t bar_base = kFullBar + 8 * (warp * STAGES);
+  int s = 0;           // stage of the next tile to consume
+  uint32_t phase = 0;  // parity of that stage's current use
+  int n_issued = 0, n_done = 0;
+  uint32_t bad_mask = 0;  // bit s: the tile now in stage s maps to no page
+  bool dead = false;      // a bounded wait gave up: stop working, keep walking to the barriers
+
+  const PageGeom geo = make_geom(BS, p.heads_kv);
+  const int n_chunks = tiles_per_page == 1 ? 7 : 9;
+  const int64_t page_bytes = p.page_stride * 4;
+  const uint32_t num_pages_u = static_cast<uint32_t>(p.num_pages);
+
+  auto wait_full = [&](uint32_t bar, uint32_t parity) -> bool {  // false: the bounded wait gave up
+    bool ok = mbar_try_wait(bar, parity);
+    if (!ok) {
+      WaitBudget budget;
+      do {
+        ok = mbar_try_wait(bar, parity);
+      } while (!ok && !budget.expired());
+    }
+    ok = __all_sync(kFull, ok);
+    if (!ok) atomicExch(&g_stream_status, 2);
+    return ok;
+  };
+
+  for (int ph = 0; ph < 2; ++ph) {
+    // ---- the part of this CTA's share that lies in its ph-th head (CTA-uniform) ------------
+    int vh = 0, span = 0, first = 0;
+    if (Tb > 0 && gb > ga) {
+      vh = static_cast<int>(ga / Tb) + ph;
+      const int64_t h0 = static_cast<int64_t>(vh) * Tb;
+      const int64_t a = max(ga, h0), e = min(gb, h0 + Tb);
+      span = e > a ? static_cast<int>(e - a) : 0;
+      first = static_cast<int>(a - h0);
+    }
+    const int range = (cta * 2 + ph) * NW + warp;
+    if (lane == 0) {
+      sp.ws_hdr[2 * range] = kHdrNone;
+      sp.ws_hdr[2 * range + 1] = kHdrNone;
+    }
+    if (span == 0) continue;
+    const int head = vh / quads, quad = vh - head * quads;
+    const int hq0 = head * gqa + quad * 4;
+    const int nh = min(4, gqa - quad * 4);
+
+    __syncthreads();  // the previous head's tables are no longer read
+    {                 // level tables -> fp16 in shared memory
+      __half* lv = reinterpret_cast<__half*>(gptr(kLevels));
+      for (int i = tid; i < 128; i += NW * 32) {
+        const int which = i >> 6, g = (i >> 4) & 3, c = i & 15;
+        lv[i] = __float2half_rn(which ? load_v_level(p, head, g, c) : load_k_level(p, head, g, c));
+      }
+    }
+    __syncthreads();
+    {  // byte -> (level[low nibble], level[high nibble]) tables, one copy per bank.
+       // Block P (P = 0, 1) holds, in bank l, the K table of group 2*((l>>1)&1)+P and the
+       // V table of group 2*(l>>4)+P: the groups lane l needs when an MMA works on pair P.
+      const unsigned short* lv = reinterpret_cast<const unsigned short*>(gptr(kLevels));
+      for (int e = warp; e < 512; e += NW) {
+        const int P = e >> 8, byte = e & 255;
+        const int kg = 2 * ((lane >> 1) & 1) + P, vg = 2 * (lane >> 4) + P;
+        const uint32_t kval = lv[kg * 16 + (byte & 15)] | (static_cast<uint32_t>(lv[kg * 16 + (byte >> 4)]) << 16);
+        const uint32_t vval = lv[64 + vg * 16 + (byte & 15)] | (static_cast<uint32_t>(lv[64 + vg * 16 + (byte >> 4)]) << 16);
+        uint32_t* row = reinterpret_cast<uint32_t*>(gptr(kLutAddr + P * kLutBlock + byte * 256));
+        row[lane] = kval;
+        row[32 + lane] = vval;
+      }
+    }
+    __syncthreads();
+    if (dead) continue;
+
+    // ---- this warp's run of tiles [wa, wb) inside the head ---------------------------------
+    const int wa = first + static_cast<int>(static_cast<int64_t>(span) * warp / NW);
+    const int wb = first + static_cast<int>(static_cast<int64_t>(span) * (warp + 1) / NW);
+    const int total = wb - wa;
+    if (total <= 0) continue;
+
+    // loader: lane c issues chunk c of a tile.  Chunks: 0/1 K codes of tokens 0-7 / 8-15
+    // (512 B each), 2 K statistics (256), 3/4 V codes (512 each), then V statistics: two
+    // 128 B chunks (groups 0-1, 2-3) for 16-token pages, else 64 B per group.
+    uint32_t ch_src = 0, ch_sub = 0, ch_dst = 0, ch_bytes = 0;
+    {
+      const uint32_t code_head = head * (BS * kWordsPerHead) * 4;
+      if (lane == 0) { ch_src = geo.k_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffKLo; ch_bytes = 512; }
+      if (lane == 1) { ch_src = geo.k_code_off * 4 + code_head + 512; ch_sub = 1024; ch_dst = kOffKHi; ch_bytes = 512; }
+      if (lane == 2) { ch_src = (geo.k_stat_off + head * (BS * 4)) * 4; ch_sub = 256; ch_dst = kOffKStat; ch_bytes = 256; }
+      if (lane == 3) { ch_src = geo.v_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffVLo; ch_bytes = 512; }
+      if (lane == 4) { ch_src = geo.v_code_off * 4 + code_head + 512; ch_sub = 1024; ch_dst = kOffVHi; ch_bytes = 512; }
+      if (lane >= 5 && lane < n_chunks) {
+        const int gg = tiles_per_page == 1 ? 2 * (lane - 5) : lane - 5;  // first group of the chunk
+        ch_src = (geo.v_stat_off + head * (4 * BS) + gg * BS) * 4;
+        ch_sub = 64;
+        ch_dst = kOffVStat + gg * 64 + (gg >= 2 ? kVStatSkew : 0);
+        ch_bytes = tiles_per_page == 1 ? 128 : 64;
+      }
+    }
+    const char* src_base = reinterpret_cast<const char*>(p.cache) + ch_src;  // this lane's chunk inside page 0
+
+    // request that holds tile x of the head (prefix[b] <= x < prefix[b+1])
+    auto request_of = [&](int x) {
+      int l = 0, h = B;
+      while (h - l > 1) {
+        const int mid = (l + h) >> 1;
+        if (prefix[mid] <= x) l = mid;
+        else h = mid;
+      }
+      return l;
+    };
+    // lane l: physical page and position in it of the (base+l)-th tile of the run
+    auto fetch_meta = [&](int base) -> uint32_t {
+      const int i = base + lane;
+      if (i >= total) return 0xFFFFFFFFu;
+      const int x = wa + i;
+      const int b = request_of(x);
+      const int k = x - prefix[b];
+      const uint32_t phys =
+          static_cast<uint32_t>(p.block_table[static_cast<int64_t>(b) * p.bt_stride + page_lo + (k >> log2r)]);
+      if (phys >= num_pages_u) return 0xFFFFFFFFu;  // also catches negative ids
+      return phys | (static_cast<uint32_t>(k & (tiles_per_page - 1)) << kMaxPagesLog2);
+    };
+    uint32_t meta_cur = fetch_meta(0), meta_nxt = fetch_meta(32);
+    auto issue = [&](int j, int stage) {  // j-th tile of the run into ring stage `stage`
+      if (j != 0 && (j & 31) == 0) {
+        meta_cur = meta_nxt;
+        meta_nxt = fetch_meta(j + 32);
+      }
+      const uint32_t meta = __shfl_sync(kFull, meta_cur, j & 31);
+      const bool bad = meta == 0xFFFFFFFFu;
+      bad_mask = bad ? (bad_mask | (1u << stage)) : (bad_mask & ~(1u << stage));
+      const uint32_t phys = bad ? 0u : (meta & ((1u << kMaxPagesLog2) - 1));
+      const uint32_t sub = bad ? 0u : (meta >> kMaxPagesLog2);
+      const uint32_t bar = bar_base + 8 * stage;
+      if (lane == 0) mbar_arrive_expect_tx(bar, kTilePayload);
+      __syncwarp();
+      if (lane < n_chunks)
+        bulk_copy_g2s(ring_base + stage * kSlotBytes + ch_dst, src_base + phys * page_bytes + sub * ch_sub, ch_bytes, bar);
+      ++n_issued;
+    };
+    if (!noload || n_issued == 0) {
+      int st = s;
+      for (int j = 0; j < min(total, STAGES); ++j) {
+        issue(j, st);
+        st = st + 1 == STAGES ? 0 : st + 1;
+      }
+    }
+
+    // ---- attention state of the request being streamed ------------------------------------
+    uint32_t qb[2][4][2];  // B operand of QK: q of head hcol, pre-scaled by softmax_scale * log2(e)
+    float qs[4];           // sum over the dims of group g of the rounded q of head tig
+    float oacc[2][4][4], cmin[2][4];
+    float m_used = -CUDART_INF_F, l_run = 0.f;  // head tig
+
+    auto process = [&](auto nt_tag, auto partial_tag, const uint32_t sbA, const uint32_t sbB, const int nvA,
+                       const int nvB) {
+      constexpr int NT = decltype(nt_tag)::value;
+      constexpr bool PARTIAL = decltype(partial_tag)::value;
+      const uint32_t sb[2] = {sbA, sbB};
+      const int nv[2] = {nvA, nvB};
+      // ------------------------------ S = Lk * Qblock (one accumulator per tile and pair) ----
+      float sacc[NT][2][4];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint32_t ka = sb[t] + kc_off;
+#pragma unroll
+        for (int P = 0; P < 2; ++P) {
+          const uint2 k0 = P ? ring_load64<16>(ka) : ring_load64<0>(ka);
+          const uint2 k1 = P ? ring_load64<16 + 256>(ka) : ring_load64<256>(ka);
+          const uint32_t w0[2] = {k0.x, k0.y}, w1[2] = {k1.x, k1.y};
+          const uint32_t kl = P ? klane1 : klane0;
+          uint32_t av[4][4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            av[j][0] = lut_load(__byte_perm(w0[j >> 1], kl, (j & 1) ? 0x7624 : 0x7604));
+            av[j][1] = lut_load(__byte_perm(w1[j >> 1], kl, (j & 1) ? 0x7624 : 0x7604));
+            av[j][2] = lut_load(__byte_perm(w0[j >> 1], kl, (j & 1) ? 0x7634 : 0x7614));
+            av[j][3] = lut_load(__byte_perm(w1[j >> 1], kl, (j & 1) ? 0x7634 : 0x7614));
+          }
+          mma16816_zero(sacc[t][P], av[0][0], av[0][1], av[0][2], av[0][3], qb[P][0][0], qb[P][0][1]);
+#pragma unroll
+          for (int j = 1; j < 4; ++j)
+            mma16816(sacc[t][P], av[j][0], av[j][1], av[j][2], av[j][3], qb[P][j][0], qb[P][j][1]);
+        }
+      }
+      // ------------------------------ V index bytes (token pair -> one table index) ---------
+      // Independent of the softmax below, so issued here to overlap with its latency.
+      uint32_t vidx[NT][2][2][2];  // [tile][pair][k-slots 2tig.. / 2tig+8..][row gid / row gid+8]
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint32_t va = sb[t] + vc_off0, vb = sb[t] + vc_off1;
+#pragma unroll
+        for (int P = 0; P < 2; ++P)
+#pragma unroll
+          for (int o = 0; o < 2; ++o) {
+            const uint32_t xa = P ? (o ? ring_load32<16 + 256>(va) : ring_load32<16>(va))
+                                  : (o ? ring_load32<256>(va) : ring_load32<0>(va));
+            const uint32_t xb = P ? (o ? ring_load32<16 + 256>(vb) : ring_load32<16>(vb))
+                                  : (o ? ring_load32<256>(vb) : ring_load32<0>(vb));
+            vidx[t][P][o][0] = (xa & 0x0F0F0F0Fu) | ((xb << 4) & 0xF0F0F0F0u);
+            vidx[t][P][o][1] = ((xa >> 4) & 0x0F0F0F0Fu) | (xb & 0xF0F0F0F0u);
+          }
+      }
+      // ------------------------------ scores of head tig for tokens tq0, tq0+4 ---------------
+      float sc[NT][2];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint32_t sa = sb[t] + ks_off;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const uint4 st = r ? ring_load128i<64>(sa) : ring_load128i<0>(sa);  // groups 0..3
+          const float2 g0 = stat_word_to_f32<STAT_BF16>(st.x), g1 = stat_word_to_f32<STAT_BF16>(st.y);
+          const float2 g2 = stat_word_to_f32<STAT_BF16>(st.z), g3 = stat_word_to_f32<STAT_BF16>(st.w);
+          float u = g0.x * sacc[t][0][2 * r];       // column 2tig: group P, column 2tig+1: group P+2
+          float v = g1.x * sacc[t][1][2 * r];
+          u = fmaf(g2.x, sacc[t][0][2 * r + 1], u);
+          v = fmaf(g3.x, sacc[t][1][2 * r + 1], v);
+          u = fmaf(g0.y, qs[0], u);
+          v = fmaf(g1.y, qs[1], v);
+          u = fmaf(g2.y, qs[2], u);
+          v = fmaf(g3.y, qs[3], v);
+          float x = u + v;
+          if (PARTIAL) {  // behind the end of the sequence (statistics may be NaN)
+            if (tq0 + 4 * r >= nv[t]) x = -CUDART_INF_F;
+          }
+          sc[t][r] = x;
+        }
+      }
+      // ------------------------------ online softmax over the tile(s) -------------------------
+      float tmax = fmaxf(sc[0][0], sc[0][1]);
+      if (NT == 2) tmax = fmaxf(tmax, fmaxf(sc[NT - 1][0], sc[NT - 1][1]));
+      tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 4));
+      tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 8));
+      tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 16));
+      const bool need = tmax > m_used + kRescaleThreshold;
+      if (__any_sync(kFull, need)) {
+        const float m_new = need ? tmax : m_used;
+        const float corr = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_used - m_new);
+        m_used = m_new;
+        l_run *= corr;
+#pragma unroll
+        for (int P = 0; P < 2; ++P) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) oacc[P][i][c] *= corr;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) cmin[P][c] *= corr;
+        }
+      }
+      uint32_t ph2[NT][2];  // [tile][k-slots 2tig.. / 2tig+8..]: probabilities of head hcol, two tokens each
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const float e0 = fast_exp2(sc[t][0] - m_used), e1 = fast_exp2(sc[t][1] - m_used);
+        l_run += e0 + e1;
+        const uint32_t mine = pack_half2(e0, e1);  // head tig: (token tq0, token tq0+4)
+        const uint32_t fromA = __shfl_sync(kFull, mine, src_lane0);  // tokens of k-slots 2tig, 2tig+8
+        const uint32_t fromB = __shfl_sync(kFull, mine, src_lane1);  // tokens of k-slots 2tig+1, 2tig+9
+        ph2[t][0] = __byte_perm(fromA, fromB, 0x5410);
+        ph2[t][1] = __byte_perm(fromA, fromB, 0x7632);
+      }
+      // ------------------------------ per tile: W = p*scale_v, p*min_v, then O += Lv^T * W ----
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        const uint32_t sa = sb[t] + vs_off;
+#pragma unroll
+        for (int P = 0; P < 2; ++P) {
+          uint32_t wb2[2], mb2[2];
+#pragma unroll
+          for (int o = 0; o < 2; ++o) {
+            const uint2 vs = P ? (o ? ring_load64<64 + 16>(sa) : ring_load64<64>(sa))
+                               : (o ? ring_load64<16>(sa) : ring_load64<0>(sa));
+            uint32_t sc2, mn2;
+            if (STAT_BF16) {
+              const uint32_t fst = pair_swapped ? vs.y : vs.x, snd = pair_swapped ? vs.x : vs.y;
+              sc2 = pack_half2(__uint_as_float(fst << 16), __uint_as_float(snd << 16));
+              mn2 = pack_half2(__uint_as_float(fst & 0xFFFF0000u), __uint_as_float(snd & 0xFFFF0000u));
+            } else {
+              sc2 = __byte_perm(vs.x, vs.y, sel_scale);
+              mn2 = __byte_perm(vs.x, vs.y, sel_min);
+            }
+            uint32_t wv = hmul2_u32(ph2[t][o], sc2), mv = hmul2_u32(ph2[t][o], mn2);
+            if (PARTIAL) {  // 0 * NaN would poison the accumulators
+              const uint32_t keep = (tk[0] + 4 * o < nv[t] ? 0x0000FFFFu : 0u) | (tk[1] + 4 * o < nv[t] ? 0xFFFF0000u : 0u);
+              wv &= keep;
+              mv &= keep;
+            }
+            wb2[o] = wv;
+            mb2[o] = mv;
+          }
+          const uint32_t vl = P ? vlane1 : vlane0;
+          uint32_t av[4][4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t sel = i == 0 ? 0x7604 : i == 1 ? 0x7614 : i == 2 ? 0x7624 : 0x7634;
+            av[i][0] = lut_load(__byte_perm(vidx[t][P][0][0], vl, sel));
+            av[i][1] = lut_load(__byte_perm(vidx[t][P][0][1], vl, sel));
+            av[i][2] = lut_load(__byte_perm(vidx[t][P][1][0], vl, sel));
+            av[i][3] = lut_load(__byte_perm(vidx[t][P][1][1], vl, sel));
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mma16816(oacc[P][i], av[i][0], av[i][1], av[i][2], av[i][3], wb2[0], wb2[1]);
+          const uint32_t ones = 0x3C003C00u;
+          mma16816(cmin[P], ones, ones, ones, ones, mb2[0], mb2[1]);
+        }
+      }
+    };
+
+    // ---- stream through the run, request by request ----------------------------------------
+    int x = wa;
+    int b = request_of(wa);
+    int run_done = 0;  // tiles of this run consumed so far
+    while (run_done < total && !dead) {
+      while (prefix[b + 1] <= x) ++b;
+      const int pb = prefix[b];
+      const int nb = prefix[b + 1] - pb;
+      const int k0 = x - pb, kend = min(nb, wb - pb);
+      const int ntok = min(p.token_hi, p.seq_lens[b]) - lo;
+      {  // query fragments and group sums of request b
+        const bool live_h = hcol < nh;
+        const int64_t qoff = static_cast<int64_t>(b) * p.q_batch_stride + static_cast<int64_t>(hq0 + hcol) * kHeadDim;
+        float part[2] = {0.f, 0.f};
+#pragma unroll
+        for (int P = 0; P < 2; ++P)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int d0 = 32 * (2 * ksel + P) + 16 * khalf + 4 * j;
+            float f[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = live_h ? load_q(p.q, qoff + d0 + i, p.q_dtype) * p.scale_log2 : 0.f;
+            const uint32_t lo2 = pack_half2(f[0], f[1]), hi2 = pack_half2(f[2], f[3]);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo2));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&hi2));
+            part[P] += (a.x + a.y) + (c.x + c.y);
+            qb[P][j][0] = ksel == gsel ? lo2 : 0u;  // the other group of the pair meets zeros
+            qb[P][j][1] = ksel == gsel ? hi2 : 0u;
+          }
+#pragma unroll
+        for (int P = 0; P < 2; ++P) {
+          part[P] += __shfl_xor_sync(kFull, part[P], 1);  // both halves of the group
+#pragma unroll
+          for (int e = 0; e < 2; ++e) qs[2 * e + P] = __shfl_sync(kFull, part[P], (2 * tig) * 4 + 2 * e);
+        }
+      }
+#pragma unroll
+      for (int P = 0; P < 2; ++P) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) oacc[P][i][c] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) cmin[P][c] = 0.f;
+      }
+      m_used = -CUDART_INF_F;
+      l_run = 0.f;
+
+      for (int k = k0; k < kend;) {
+        const int cnt = min(2, kend - k);
+        const int sB = s + 1 == STAGES ? 0 : s + 1;
+        const uint32_t phaseB = s + 1 == STAGES ? phase ^ 1u : phase;
+        // (the timing experiment stops issuing after the first fill and so stops waiting too)
+        if (n_done < n_issued && !wait_full(bar_base + 8 * s, phase)) { dead = true; break; }
+        if (cnt == 2 && n_done + 1 < n_issued && !wait_full(bar_base + 8 * sB, phaseB)) { dead = true; break; }
+        const int rem = ntok - kTile * k;
+        const int nvA = (bad_mask >> s) & 1 ? 0 : min(kTile, rem);
+        const int nvB = cnt == 2 ? ((bad_mask >> sB) & 1 ? 0 : min(kTile, rem - kTile)) : 0;
+        const uint32_t sbA = ring_base + s * kSlotBytes, sbB = ring_base + sB * kSlotBytes;
+        if (cnt == 2) {
+          if (nvA == kTile && nvB == kTile)
+            process(std::integral_constant<int, 2>{}, std::false_type{}, sbA, sbB, nvA, nvB);
+          else if (nvA > 0 || nvB > 0)
+            process(std::integral_constant<int, 2>{}, std::true_type{}, sbA, sbB, nvA, nvB);
+        } else if (nvA > 0) {
+          process(std::integral_constant<int, 1>{}, std::true_type{}, sbA, sbA, nvA, 0);
+        }
+        // the stages are free again: refill them with the tiles STAGES ahead
+        if (!noload) {
+          __syncwarp();
+          fence_proxy_async();
+          if (run_done + STAGES < total) issue(run_done + STAGES, s);
+          if (cnt == 2 && run_done + 1 + STAGES < total) issue(run_done + 1 + STAGES, sB);
+        }
+        k += cnt;
+        run_done += cnt;
+        n_done += cnt;
+        if (cnt == 2) {
+          s = sB + 1 == STAGES ? 0 : sB + 1;
+          phase = sB + 1 == STAGES ? phaseB ^ 1u : phaseB;
+        } else {
+          s = sB;
+          phase = phaseB;
+        }
+      }
+      if (dead) break;
+
+      // ---- leave request b: final output or a partial ---------------------------------------
+      float l_tot = l_run;  // tokens were spread over gid
+      l_tot += __shfl_xor_sync(kFull, l_tot, 4);
+      l_tot += __shfl_xor_sync(kFull, l_tot, 8);
+      l_tot += __shfl_xor_sync(kFull, l_tot, 16);
+      const bool whole = k0 == 0 && kend == nb;
+      if (tig < nh) {
+        if (whole) {
+          const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+          const int64_t row = static_cast<int64_t>(b) * p.heads_q + hq0 + tig;
+#pragma unroll
+          for (int P = 0; P < 2; ++P)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int d = 32 * (2 * vsel + P) + 8 * vu + 2 * i;
+              const float mn = vsel ? cmin[P][1] : cmin[P][0];
+              const float ve = ((vsel ? oacc[P][i][1] : oacc[P][i][0]) + mn) * inv;
+              const float vo = ((vsel ? oacc[P][i][3] : oacc[P][i][2]) + mn) * inv;
+              store_out(p.out, row * kHeadDim + d, p.out_dtype, ve);
+              store_out(p.out, row * kHeadDim + d + 1, p.out_dtype, vo);
+              if (p.out_f32) {
+                p.out_f32[row * kHeadDim + d] = ve;
+                p.out_f32[row * kHeadDim + d + 1] = vo;
+              }
+            }
+        } else {
+          const int64_t row = static_cast<int64_t>(2 * range + (k0 > 0 ? 0 : 1)) * 4 + tig;
+          float2* dst = reinterpret_cast<float2*>(sp.ws_o + row * kHeadDim);
+#pragma unroll
+          for (int P = 0; P < 2; ++P)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int d = 32 * (2 * vsel + P) + 8 * vu + 2 * i;
+              const float mn = vsel ? cmin[P][1] : cmin[P][0];
+              dst[d >> 1] = make_float2((vsel ? oacc[P][i][1] : oacc[P][i][0]) + mn,
+                                        (vsel ? oacc[P][i][3] : oacc[P][i][2]) + mn);
+            }
+          if (gid == 0) {
+            sp.ws_m[row] = m_used;
+            sp.ws_l[row] = l_tot;
+          }
+        }
+      }
+      if (!whole && lane == 0)
+        sp.ws_hdr[2 * range + (k0 > 0 ? 0 : 1)] = ((vh * B + b) << 1) | (kend == nb ? 1 : 0);
+      x += kend - k0;
+    }
+  }
+
+  if (dead) {  // let the copies still in flight land before the shared memory is given back
+    for (int g = n_done; g < n_issued; ++g) {
+      const int st = g % STAGES;
+      WaitBudget budget;
+      while (!mbar_try_wait(bar_base + 8 * st, (g / STAGES) & 1) && !budget.expired()) {
+      }
+    }
+  }
+}
+
+// ---- fix-up: merge the chains of partials of the requests that were cut ---------------------
+// One CTA per (range, query head of the quad); it owns the request whose FIRST part is slot 1
+// of its range and walks the following ranges' slot 0 until the part flagged last.
+constexpr int kFixThreads = 128;
+constexpr int kFixBatch = 8;
+
+__global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamParams sp, const int num_ranges) {
+  const DecodeParams& p = sp.d;
+  const int range = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const int hd = sp.ws_hdr[2 * range + 1];
+  if (hd < 0) return;
+  const int item = hd >> 1;
+  const int vh = item / p.batch, b = item - vh * p.batch;
+  const int head = vh / sp.quads, quad = vh - head * sp.quads;
+  const int gqa = p.heads_q / p.heads_kv;
+  if (h >= min(4, gqa - quad * 4)) return;
+
+  __shared__ int s_hdr[kFixThreads];
+  __shared__ int s_list[kFixThreads];
+  __shared__ int s_cnt, s_done;
+
+  float M = -CUDART_INF_F, num = 0.f, den = 0.f;
+  auto merge = [&](float m2, float l2, float o2) {
+    if (!(l2 > 0.f)) return;
+    const float Mn = fmaxf(M, m2);
+    const float a = (M == -CUDART_INF_F) ? 0.f : exp2f(M - Mn);
+    const float w = exp2f(m2 - Mn);
+    num = num * a + o2 * w;
+    den = den * a + l2 * w;
+    M = Mn;
+  };
+  {
+    const int64_t row = static_cast<int64_t>(2 * range + 1) * 4 + h;
+    merge(sp.ws_m[row], sp.ws_l[row], sp.ws_o[row * kHeadDim + d]);
+  }
+  const bool chain_open = (hd & 1) == 0;
+  for (int base = range + 1; chain_open && base < num_ranges; base += kFixThreads) {
+    const int r = base + d;
+    s_hdr[d] = r < num_ranges ? sp.ws_hdr[2 * r] : kHdrNone;
+    __syncthreads();
+    if (d == 0) {
+      int cnt = 0, done = base + kFixThreads >= num_ranges ? 1 : 0;
+      for (int j = 0; j < kFixThreads; ++j) {
+        const int hj = s_hdr[j];
+        if (hj < 0) continue;            // an empty range
+        if ((hj >> 1) != item) { done = 1; break; }  // cannot happen: the chain is contiguous
+        s_list[cnt++] = base + j;
+        if (hj & 1) { done = 1; break; }
+      }
+      s_cnt = cnt;
+      s_done = done;
+    }
+    __syncthreads();
+    const int cnt = s_cnt;
+    for (int c0 = 0; c0 < cnt; c0 += kFixBatch) {
+      float m2[kFixBatch], l2[kFixBatch], o2[kFixBatch];
+#pragma unroll
+      for (int u = 0; u < kFixBatch; ++u) {
+        l2[u] = 0.f;
+        m2[u] = 0.f;
+        o2[u] = 0.f;
+        if (c0 + u < cnt) {
+          const int64_t row = static_cast<int64_t>(2 * s_list[c0 + u]) * 4 + h;
+          m2[u] = sp.ws_m[row];
+          l2[u] = sp.ws_l[row];
+          o2[u] = sp.ws_o[row * kHeadDim + d];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kFixBatch; ++u) merge(m2[u], l2[u], o2[u]);
+    }
+    const int done = s_done;
+    __syncthreads();
+    if (done) break;
+  }
+  const float o = den > 0.f ? num / den : 0.f;
+  const int64_t row = static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4 + h;
+  store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
+  if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
+}
+
+constexpr int64_t kPartialBytes = 4 * kHeadDim * 4 + 16 + 16 + 4;  // o, m, l of four heads and the header
+
+template <int NW, int STAGES>
+int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_seq_len, int sm_count,
+                   cudaStream_t stream) {
+  using R = Ring<NW, STAGES>;
+  StreamParams sp;
+  sp.d = p;
+  const int gqa = p.heads_q / p.heads_kv;
+  sp.quads = (gqa + 3) / 4;
+  const int hv = p.heads_kv * sp.quads;
+  if (hv > sm_count) return BKV_ERR_UNSUPPORTED;
+  const int64_t tiles_max = static_cast<int64_t>(hv) * p.batch * ((max_seq_len + kTile - 1) / kTile);
+  int64_t ctas = (tiles_max + 2 * NW - 1) / (2 * NW);
+  if (ctas < hv) ctas = hv;  // a share never spans more than two heads
+  if (ctas > sm_count) ctas = sm_count;
+  const int C = static_cast<int>(ctas);
+  const int num_ranges = C * 2 * NW;
+  const int64_t slots = 2ll * num_ranges;
+  if (!ws || ws_bytes < slots * kPartialBytes) return BKV_ERR_ARG;
+  char* w = static_cast<char*>(ws);
+  sp.ws_o = reinterpret_cast<float*>(w);
+  sp.ws_m = reinterpret_cast<float*>(w + slots * (4 * kHeadDim * 4));
+  sp.ws_l = sp.ws_m + slots * 4;
+  sp.ws_hdr = reinterpret_cast<int*>(sp.ws_l + slots * 4);
+
+  auto kern = p.stat_bf16 ? decode_stream_kernel<NW, STAGES, true> : decode_stream_kernel<NW, STAGES, false>;
+  static bool configured[2][64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[p.stat_bf16 ? 1 : 0][dev]) {
+    int reserved = 0;
+    cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev);
+    if (reserved != static_cast<int>(kSmemBase)) return BKV_ERR_UNSUPPORTED;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, R::kDynBytes);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(e, "cudaFuncSetAttribute(decode_stream_kernel)");
+      return BKV_ERR_CUDA;
+    }
+    configured[p.stat_bf16 ? 1 : 0][dev] = true;
+  }
+  kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp);
+  int rc = check_launch("bkv_decode_stream_sm100(decode)");
+  if (rc != BKV_OK) return rc;
+  stream_fixup_kernel<<<dim3(num_ranges, 4), kFixThreads, 0, stream>>>(sp, num_ranges);
+  return check_launch("bkv_decode_stream_sm100(fixup)");
+}
+
+int device_sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && cached[dev]) return cached[dev];
+  int n = 0;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (dev < 64) cached[dev] = n;
+  return n;
+}
+
+}  // namespace
+
+int64_t stream_workspace_bytes() {
+  const int64_t sms = device_sm_count();
+  return sms * 2 * 16 * 2 * kPartialBytes;  // ranges of the widest configuration (16 warps), two slots each
+}
+
+int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_seq_len, cudaStream_t stream,
+                         int config) {
+  const int r = p.block_size / kTile;
+  if (p.block_size % kTile != 0 || (r & (r - 1)) != 0 || p.block_size > 1024) return BKV_ERR_UNSUPPORTED;
+  if ((p.page_stride * 4) % 16 != 0 || !aligned16(p.cache)) return BKV_ERR_UNSUPPORTED;
+  if (p.token_lo % p.block_size != 0) return BKV_ERR_UNSUPPORTED;
+  if (p.batch > kMaxBatch || p.num_pages > (1ll << kMaxPagesLog2)) return BKV_ERR_UNSUPPORTED;
+  const int sms = device_sm_count();
+  if (sms <= 0) return BKV_ERR_CUDA;
+  switch (config) {
+    case 1: return launch_variant<8, 4>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 3: return launch_variant<16, 2>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    default: return launch_variant<12, 3>(p, ws, ws_bytes, max_seq_len, sms, stream);
+  }
+}
+
+int read_stream_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_stream_status, sizeof(int));
+  const int zero = 0;
+  cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int));
+  return v;
+}
+
+}  // namespace bkv

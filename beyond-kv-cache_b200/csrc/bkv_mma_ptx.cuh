@@ -1,0 +1,178 @@
+// PTX wrappers and the shared-memory tile format used by the tensor-core decode kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include <cstdint>
+
+namespace bkv {
+namespace mma {
+
+// ---- one 16-token tile of one KV head in a ring slot ---------------------------------
+// K codes (16 x 64 B), K statistics (16 x 16 B), V codes (16 x 64 B), V statistics
+// (4 groups x 16 tokens x 4 B).  The code rows of tokens 8-15 start kCodeSkew bytes later
+// than contiguous, which makes the per-lane code loads of the MMA layouts conflict-free.
+constexpr int kTile = 16;
+constexpr int kCodeSkew = 16;
+constexpr int kOffKLo = 0;
+constexpr int kOffKHi = 512 + kCodeSkew;
+constexpr int kOffKStat = kOffKHi + 512;
+constexpr int kOffVLo = kOffKStat + 256;
+constexpr int kOffVHi = kOffVLo + 512 + kCodeSkew;
+constexpr int kOffVStat = kOffVHi + 512;
+constexpr int kTileBytes = kOffVStat + 256;  // 2592
+constexpr int kTilePayload = 2560;           // bytes the bulk copies of one tile deliver
+
+// ---- shared-memory map of a CTA that owns the SM ---------------------------------------
+constexpr uint32_t kSmemBase = 0x400;              // dynamic shared memory starts after the 1 KB the system reserves
+constexpr uint32_t kSmemEnd = kSmemBase + 232448;  // 227 KB opt-in maximum
+constexpr uint32_t kLutAddr = 0x10000;  // table block P at kLutAddr + P*kLutBlock: address = block | byte << 8 | slot
+constexpr uint32_t kLutBlock = 0x10000;
+constexpr uint32_t kRingHi = kLutAddr + 2 * kLutBlock;
+constexpr int kCtrlBytes = 2048;  // barriers, fp16 level tables
+constexpr uint32_t kRingLo = kSmemBase + kCtrlBytes;
+constexpr int kLoSlots = (kLutAddr - kRingLo) / kTileBytes;
+
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait that lasts 2 s gives up
+constexpr float kRescaleThreshold = 8.f;                     // log2 units: p stays below 2^8
+// token held by k-slot n of the PV MMAs (nibble n): 0,1,3,2, 8,9,11,10, 4,5,7,6, 12,13,15,14
+constexpr unsigned long long kTokOfSlot = 0xEFDC6754AB982310ull;
+// QK MMA row g (and g+8) carries the token of k-slot kRowSlot[g] (and +8): 0,1,4,5,2,3,6,7 (an involution)
+constexpr uint32_t kRowSlot = 0x76325410u;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait bookkeeping: true once kWaitLimitNs have passed since the first failed
+// poll (the clock is only read every 256 polls).
+struct WaitBudget {
+  uint32_t polls = 0;
+  unsigned long long start = 0;
+  __device__ __forceinline__ bool expired() {
+    if ((++polls & 255u) != 0) return false;
+    const unsigned long long now = global_timer_ns();
+    if (start == 0) {
+      start = now;
+      return false;
+    }
+    return now - start > kWaitLimitNs;
+  }
+  __device__ __forceinline__ void reset() {
+    polls = 0;
+    start = 0;
+  }
+};
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma16816_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {  // c = a*b (no accumulator input)
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: 2 ulp, exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// Table look-up: the address is complete, no base is added.  Not volatile: the table is
+// constant once built, so the compiler may schedule these freely.
+__device__ __forceinline__ uint32_t lut_load(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+// Ring loads are volatile: they stay, in program order, between the full-barrier wait of
+// their tile and the bulk copies that later refill the same ring stage.
+__device__ __forceinline__ uint4 ring_load128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint4 ring_load128i(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr), "n"(IMM));
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint2 ring_load64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0,%1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(IMM));
+  return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint32_t ring_load32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+  return v;
+}
+template <bool BF16>
+__device__ __forceinline__ float2 stat_word_to_f32(uint32_t w) {  // (scale, minimum)
+  if (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+// byte offset of token t's 64-byte code row inside a K or V code area of a tile
+__host__ __device__ constexpr int code_row_off(int t) { return t * 64 + (t >= 8 ? kCodeSkew : 0); }
+
+// registers a thread may use when one CTA of NW warps owns the SM: the register file is
+// split over the four schedulers (16 K registers each) and a CTA's warps are dealt to them
+// round-robin
+constexpr int max_regs_for(int nw) {
+  const int per_thread = 16384 / (((nw + 3) / 4) * 32) / 8 * 8;
+  return per_thread > 255 ? 255 : per_thread;
+}
+
+}  // namespace mma
+}  // namespace bkv

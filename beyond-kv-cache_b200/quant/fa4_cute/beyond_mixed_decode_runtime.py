@@ -242,11 +242,24 @@ def allocate_runtime_workspace(spec: DecodeRuntimeSpec, *, device: torch.device)
     """Allocate the split workspace once, before any CUDA-graph capture
     (reference :305-324).  All three tensors are float32."""
     partial_shape = (spec.num_splits, spec.batch_size, spec.heads_q, 1, _HEAD_DIM)
-    return {
+    ws = {
         "o_partial": torch.empty(partial_shape, dtype=torch.float32, device=device),
         "m_partial": torch.empty(partial_shape[:-1], dtype=torch.float32, device=device),
         "l_partial": torch.empty(partial_shape[:-1], dtype=torch.float32, device=device),
     }
+    if stream_schedule_supported(spec):
+        # scratch of the persistent schedule (partials of requests cut between workers);
+        # its size depends on the device only
+        with torch.cuda.device(device):
+            nbytes = int(_lib.load().bkv_decode_stream_workspace_bytes())
+        ws["stream"] = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    return ws
+
+
+def stream_schedule_supported(spec: DecodeRuntimeSpec) -> bool:
+    """The persistent schedule (``bkv_decode_stream_sm100``) keeps a per-request table in
+    shared memory and packs page ids into 26 bits; larger buckets use the split grid."""
+    return spec.batch_size <= 1024 and spec.physical_pages <= (1 << 26)
 
 
 def _validate_launch_tensors(*, spec, q, out, block_table, seq_lens, k_qpoints_lane_major, v_qpoints_code_major, workspace) -> None:
@@ -324,6 +337,25 @@ def run_nonuniform_decode(
         raise ValueError("out_f32 must be a contiguous float32 tensor of the output size")
     stat = stat_dtype if stat_dtype is not None else q.dtype
     flags = _lib.FLAG_KLEVELS_LANE_MAJOR | (_lib.FLAG_PDL_WAIT if spec.wait_for_pdl_writer else 0)
+    use_stream = (variant == 0 or variant >= 40) and "stream" in workspace and stream_schedule_supported(spec)
+    if use_stream:
+        scratch = workspace["stream"]
+        _lib.call(
+            "bkv_decode_stream_sm100",
+            q.data_ptr(), spec.q_batch_stride, _lib.dtype_code(q.dtype),
+            cache.data_ptr(), spec.physical_pages, spec.packed_page_stride_i32, spec.page_size,
+            spec.heads_kv, _lib.dtype_code(stat),
+            block_table.data_ptr(), spec.page_table_stride, seq_lens.data_ptr(),
+            k_qpoints_lane_major.data_ptr(), v_qpoints_code_major.data_ptr(),
+            _lib.dtype_code(k_qpoints_lane_major.dtype),
+            out.data_ptr(), _lib.dtype_code(out.dtype), _lib.ptr(out_f32),
+            scratch.data_ptr(), int(scratch.numel()),
+            spec.batch_size, spec.heads_q, spec.max_seq_len,
+            float(softmax_scale), flags, int(variant), _lib.current_stream(q.device),
+        )
+        return out
+    if variant >= 40:
+        raise ValueError("the persistent schedule was requested but this bucket does not support it")
     multi = spec.num_splits > 1
     _lib.call(
         "bkv_decode_sm100",

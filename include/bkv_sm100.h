@@ -111,6 +111,35 @@ int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const v
                      bkv_stream_t stream);
 
 /*
+ * Persistent form of bkv_decode_sm100: same inputs and results, different schedule.
+ *
+ * Replaces the same reference launcher as bkv_decode_sm100
+ * (quant/fa4_cute/beyond_mixed_decode_runtime.py:255-330 run_nonuniform_decode ->
+ * compiled split kernel + combine).  Instead of a (split, head, request) grid whose split
+ * count comes from the launch policy, one CTA per SM takes an equal share of all
+ * (head, request, tile) work, so requests of any length mix keep every SM busy and the
+ * decode tables are built once per CTA.  Requests that end up cut between workers leave
+ * partials in `workspace`; a second kernel merges them.  num_splits does not exist here.
+ *
+ * workspace / workspace_bytes: device scratch of at least
+ * bkv_decode_stream_workspace_bytes() bytes (the bound depends on the current device
+ * only, not on the shapes); contents need not be initialised and are overwritten.
+ * Two calls that may overlap on the GPU need separate workspaces.
+ * Returns BKV_ERR_UNSUPPORTED (launch nothing) for batch > 1024, more than 2^26 pages or
+ * a page size the tensor-core kernel does not handle; use bkv_decode_sm100 then.
+ * variant: 0 default configuration; 41 / 43 select 8 / 16 warps per CTA.
+ */
+int64_t bkv_decode_stream_workspace_bytes(void);
+int bkv_decode_stream_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const void* cache,
+                            int64_t num_pages, int64_t page_stride_i32, int block_size,
+                            int heads_kv, int stat_dtype, const int32_t* block_table,
+                            int64_t block_table_stride, const int32_t* seq_lens,
+                            const void* lvl_k, const void* lvl_v, int table_dtype, void* out,
+                            int out_dtype, float* out_f32, void* workspace,
+                            int64_t workspace_bytes, int batch, int heads_q, int max_seq_len,
+                            float softmax_scale, int flags, int variant, bkv_stream_t stream);
+
+/*
  * bkv_decode_sm100 for callers that cannot allocate device memory (no counterpart in
  * the reference, whose launcher always receives a caller-allocated workspace).
  *

@@ -47,7 +47,7 @@ def _check(q, cache, bt, lens, heads_kv, bs, lk, lv, kind, **kw):
     return err, spec
 
 
-@pytest.mark.parametrize("variant", [1, 0])
+@pytest.mark.parametrize("variant", [1, 0, 20])
 def test_config0_against_reference_output(golden, variant):
     """Config 0 (float32 Q, fp16 statistics): the numbers the reference's own code
     produced (fp32 SDPA over its read-back cache), within 2e-3, straight through the
@@ -77,7 +77,7 @@ def test_config0_against_reference_output(golden, variant):
     _check(qb, cache, bt, [1024] * 4, 8, 16, lk, lv, "f16", variant=variant)
 
 
-@pytest.mark.parametrize("variant", [1, 0])
+@pytest.mark.parametrize("variant", [1, 0, 20])
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
 @pytest.mark.parametrize("bs,gqa,heads_kv", [(16, 4, 8), (64, 4, 2), (128, 8, 2), (32, 2, 4), (16, 1, 4)])
 def test_ragged_batch(bs, gqa, heads_kv, kind, variant):
@@ -92,7 +92,7 @@ def test_ragged_batch(bs, gqa, heads_kv, kind, variant):
     assert not out[0].any() and not out32[0].any()  # seq_len 0 -> zeros
 
 
-@pytest.mark.parametrize("variant", [1, 0])
+@pytest.mark.parametrize("variant", [1, 0, 20])
 def test_long_context_many_splits(variant):
     lens = [16 * 1024 + 5, 9000]
     lk, tk, lv, tv = tables(2, 3)
@@ -100,6 +100,23 @@ def test_long_context_many_splits(variant):
     q = torch.from_numpy(np.random.default_rng(2).standard_normal((2, 8, 128)).astype(np.float32)).to(torch.bfloat16)
     for splits in (1, 7, 32):
         _check(q, cache, bt, lens, 2, 16, lk, lv, "bf16", splits=splits, variant=variant)
+
+
+@pytest.mark.parametrize("variant", [40, 41, 43])
+@pytest.mark.parametrize("bs,heads_kv,gqa,kind", [(16, 2, 4, "bf16"), (64, 4, 8, "f16"), (32, 3, 2, "bf16")])
+def test_persistent_schedule_cut_requests(bs, heads_kv, gqa, kind, variant):
+    """Many ragged requests under the persistent schedule: workers cut requests at arbitrary
+    tiles, so whole-request outputs, two-part and many-part chains of partials and empty
+    requests all occur in one launch (8, 12 and 16 warps per CTA)."""
+    rng = np.random.default_rng(100 + bs)
+    lens = [int(v) for v in rng.integers(0, 900, size=37)]
+    lens[3], lens[11], lens[20], lens[36] = 0, 4100, 1, 2500
+    lk, tk, lv, tv = tables(heads_kv, 31)
+    cache, bt = oracle_cache(lens, heads_kv, bs, kind, 55, tk.float().numpy(), tv.float().numpy())
+    q = torch.from_numpy(rng.standard_normal((len(lens), heads_kv * gqa, 128)).astype(np.float32)).to(KIND_TO_DTYPE[kind])
+    _check(q, cache, bt, lens, heads_kv, bs, lk, lv, kind, variant=variant)
+    out, out32, _ = gpu_decode(q, cache, bt, lens, heads_kv, bs, lk, lv, kind=kind, variant=variant)
+    assert not out[3].any() and not out32[3].any()  # seq_len 0 -> zeros
 
 
 def test_fused_qkv_query_view_and_bucket_truncation():
