@@ -63,6 +63,55 @@ struct StreamParams {
   int quads;     // query-head quads per kv head
 };
 
+// All bulk copies of one tile, issued by one elected lane of a converged warp in a single
+// predicated block (operands are warp-uniform).  Destination offsets follow the tile format.
+static_assert(kTilePayload == 2560 && kOffKHi == 528 && kOffKStat == 1040 && kOffVLo == 1296 && kOffVHi == 1824 &&
+                  kOffVStat == 2336 && kVStatSkew == 16,
+              "the offsets below are written out in the PTX text");
+__device__ __forceinline__ void issue_tile_page16(uint32_t dst, uint32_t bar, const char* kc, const char* ks,
+                                                  const char* vc, const char* vs) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], 2560;\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%2], 512, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+528], [%2+512], 512, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1040], [%3], 256, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1296], [%4], 512, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1824], [%4+512], 512, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2336], [%5], 128, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2480], [%5+128], 128, [%1];\n"
+      "}\n" ::"r"(dst),
+      "r"(bar), "l"(kc), "l"(ks), "l"(vc), "l"(vs)
+      : "memory");
+}
+// pages of more than 16 tokens: the V statistics of the four groups are `group_stride` bytes apart
+__device__ __forceinline__ void issue_tile_paged(uint32_t dst, uint32_t bar, const char* kc, const char* ks,
+                                                 const char* vc, const char* vs, int64_t group_stride) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 v1, v2, v3;\n"
+      "add.s64 v1, %5, %6;\n"
+      "add.s64 v2, v1, %6;\n"
+      "add.s64 v3, v2, %6;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], 2560;\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%2], 512, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+528], [%2+512], 512, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1040], [%3], 256, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1296], [%4], 512, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1824], [%4+512], 512, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2336], [%5], 64, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2400], [v1], 64, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2480], [v2], 64, [%1];\n"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2544], [v3], 64, [%1];\n"
+      "}\n" ::"r"(dst),
+      "r"(bar), "l"(kc), "l"(ks), "l"(vc), "l"(vs), "l"(group_stride)
+      : "memory");
+}
+
 template <int NW, int STAGES>
 struct Ring {
   static_assert(NW * STAGES <= 64, "control block holds at most 64 barriers");
@@ -75,8 +124,12 @@ struct Ring {
   }
 };
 
-template <int NW, int STAGES, bool STAT_BF16>
+// LOADER 0: bulk copies (cp.async.bulk) completing on one mbarrier per ring stage, issued by an
+// elected lane.  LOADER 1: every lane moves 16-byte pieces with cp.async, one commit group per
+// tile; the pieces land wherever the tile format wants them, at a fifth of the instructions.
+template <int NW, int STAGES, bool STAT_BF16, int LOADER>
 __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamParams sp) {
+  static_assert(STAGES <= 4, "cp_async_wait_pending handles up to three groups in flight");
   using R = Ring<NW, STAGES>;
   const DecodeParams& p = sp.d;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -86,7 +139,10 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
   }
   auto gptr = [&](uint32_t shared_addr) { return smem + (shared_addr - kSmemBase); };
   constexpr uint32_t kFull = 0xffffffffu;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31;
+  // broadcast from lane 0 so that the compiler knows the warp index (and all the loop state
+  // derived from it) to be uniform across the warp
+  const int warp = __shfl_sync(kFull, tid >> 5, 0);
   const int gid = lane >> 2, tig = lane & 3;
   const int C = gridDim.x, cta = blockIdx.x;
   const int B = p.batch;
@@ -187,7 +243,6 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
   bool dead = false;      // a bounded wait gave up: stop working, keep walking to the barriers
 
   const PageGeom geo = make_geom(BS, p.heads_kv);
-  const int n_chunks = tiles_per_page == 1 ? 7 : 9;
   const int64_t page_bytes = p.page_stride * 4;
   const uint32_t num_pages_u = static_cast<uint32_t>(p.num_pages);
 
@@ -256,26 +311,30 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
     const int total = wb - wa;
     if (total <= 0) continue;
 
-    // loader: lane c issues chunk c of a tile.  Chunks: 0/1 K codes of tokens 0-7 / 8-15
-    // (512 B each), 2 K statistics (256), 3/4 V codes (512 each), then V statistics: two
-    // 128 B chunks (groups 0-1, 2-3) for 16-token pages, else 64 B per group.
-    uint32_t ch_src = 0, ch_sub = 0, ch_dst = 0, ch_bytes = 0;
-    {
-      const uint32_t code_head = head * (BS * kWordsPerHead) * 4;
-      if (lane == 0) { ch_src = geo.k_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffKLo; ch_bytes = 512; }
-      if (lane == 1) { ch_src = geo.k_code_off * 4 + code_head + 512; ch_sub = 1024; ch_dst = kOffKHi; ch_bytes = 512; }
-      if (lane == 2) { ch_src = (geo.k_stat_off + head * (BS * 4)) * 4; ch_sub = 256; ch_dst = kOffKStat; ch_bytes = 256; }
-      if (lane == 3) { ch_src = geo.v_code_off * 4 + code_head; ch_sub = 1024; ch_dst = kOffVLo; ch_bytes = 512; }
-      if (lane == 4) { ch_src = geo.v_code_off * 4 + code_head + 512; ch_sub = 1024; ch_dst = kOffVHi; ch_bytes = 512; }
-      if (lane >= 5 && lane < n_chunks) {
-        const int gg = tiles_per_page == 1 ? 2 * (lane - 5) : lane - 5;  // first group of the chunk
-        ch_src = (geo.v_stat_off + head * (4 * BS) + gg * BS) * 4;
-        ch_sub = 64;
-        ch_dst = kOffVStat + gg * 64 + (gg >= 2 ? kVStatSkew : 0);
-        ch_bytes = tiles_per_page == 1 ? 128 : 64;
-      }
+    // loader: one lane issues the bulk copies of a tile, so every operand is warp-uniform.
+    // Chunks: K codes of tokens 0-7 / 8-15 (512 B each), K statistics (256), V codes (512
+    // each), then V statistics: two 128 B chunks (groups 0-1, 2-3) for 16-token pages, else
+    // 64 B per group.
+    const uint32_t code_head = head * (BS * kWordsPerHead) * 4;
+    const char* const kc_src = reinterpret_cast<const char*>(p.cache) + geo.k_code_off * 4 + code_head;
+    const char* const ks_src = reinterpret_cast<const char*>(p.cache) + (geo.k_stat_off + head * (BS * 4)) * 4;
+    const char* const vc_src = reinterpret_cast<const char*>(p.cache) + geo.v_code_off * 4 + code_head;
+    const char* const vs_src = reinterpret_cast<const char*>(p.cache) + (geo.v_stat_off + head * (4 * BS)) * 4;
+    // cp.async loader: lane l moves the l-th 16 bytes of each 512-byte half of the K and V
+    // codes; lanes 0-15 move the K statistics, lanes 16-31 the V statistics
+    const uint32_t ld_kcode = geo.k_code_off * 4 + code_head + lane * 16;
+    const uint32_t ld_vcode = geo.v_code_off * 4 + code_head + lane * 16;
+    uint32_t ld_stat_src, ld_stat_dst, ld_stat_sub;
+    if (lane < 16) {
+      ld_stat_src = (geo.k_stat_off + head * (BS * 4)) * 4 + lane * 16;
+      ld_stat_dst = kOffKStat + lane * 16;
+      ld_stat_sub = 256;
+    } else {
+      const int g = (lane - 16) >> 2, c = (lane - 16) & 3;  // 64 bytes per group and tile
+      ld_stat_src = (geo.v_stat_off + head * (4 * BS) + g * BS) * 4 + c * 16;
+      ld_stat_dst = kOffVStat + g * 64 + c * 16 + (g >= 2 ? kVStatSkew : 0);
+      ld_stat_sub = 64;
     }
-    const char* src_base = reinterpret_cast<const char*>(p.cache) + ch_src;  // this lane's chunk inside page 0
 
     // request that holds tile x of the head (prefix[b] <= x < prefix[b+1])
     auto request_of = [&](int x) {
@@ -310,11 +369,29 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
       bad_mask = bad ? (bad_mask | (1u << stage)) : (bad_mask & ~(1u << stage));
       const uint32_t phys = bad ? 0u : (meta & ((1u << kMaxPagesLog2) - 1));
       const uint32_t sub = bad ? 0u : (meta >> kMaxPagesLog2);
-      const uint32_t bar = bar_base + 8 * stage;
-      if (lane == 0) mbar_arrive_expect_tx(bar, kTilePayload);
-      __syncwarp();
-      if (lane < n_chunks)
-        bulk_copy_g2s(ring_base + stage * kSlotBytes + ch_dst, src_base + phys * page_bytes + sub * ch_sub, ch_bytes, bar);
+      const uint32_t dst = ring_base + stage * kSlotBytes;
+      const int64_t pg = phys * page_bytes;
+      if (LOADER == 1) {
+        if (!bad) {
+          const char* const page = reinterpret_cast<const char*>(p.cache) + pg;
+          const char* const kp = page + (ld_kcode + sub * 1024);
+          const char* const vp = page + (ld_vcode + sub * 1024);
+          const uint32_t dl = dst + lane * 16;
+          cp_async16(dl + kOffKLo, kp);
+          cp_async16(dl + kOffKHi, kp + 512);
+          cp_async16(dst + ld_stat_dst, page + (ld_stat_src + sub * ld_stat_sub));
+          cp_async16(dl + kOffVLo, vp);
+          cp_async16(dl + kOffVHi, vp + 512);
+        }
+        cp_async_commit();
+      } else {
+        const uint32_t bar = bar_base + 8 * stage;
+        if (tiles_per_page == 1)
+          issue_tile_page16(dst, bar, kc_src + pg, ks_src + pg, vc_src + pg, vs_src + pg);
+        else
+          issue_tile_paged(dst, bar, kc_src + pg + sub * 1024, ks_src + pg + sub * 256, vc_src + pg + sub * 1024,
+                           vs_src + pg + sub * 64, static_cast<int64_t>(BS) * 4);
+      }
       ++n_issued;
     };
     if (!noload || n_issued == 0) {
@@ -538,8 +615,15 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
         const int sB = s + 1 == STAGES ? 0 : s + 1;
         const uint32_t phaseB = s + 1 == STAGES ? phase ^ 1u : phase;
         // (the timing experiment stops issuing after the first fill and so stops waiting too)
-        if (n_done < n_issued && !wait_full(bar_base + 8 * s, phase)) { dead = true; break; }
-        if (cnt == 2 && n_done + 1 < n_issued && !wait_full(bar_base + 8 * sB, phaseB)) { dead = true; break; }
+        if (LOADER == 1) {
+          if (n_done < n_issued) {
+            cp_async_wait_pending(n_issued - n_done - cnt);  // this thread's pieces of the tile(s) ...
+            __syncwarp();                                     // ... and every other lane's
+          }
+        } else {
+          if (n_done < n_issued && !wait_full(bar_base + 8 * s, phase)) { dead = true; break; }
+          if (cnt == 2 && n_done + 1 < n_issued && !wait_full(bar_base + 8 * sB, phaseB)) { dead = true; break; }
+        }
         const int rem = ntok - kTile * k;
         const int nvA = (bad_mask >> s) & 1 ? 0 : min(kTile, rem);
         const int nvB = cnt == 2 ? ((bad_mask >> sB) & 1 ? 0 : min(kTile, rem - kTile)) : 0;
@@ -555,7 +639,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
         // the stages are free again: refill them with the tiles STAGES ahead
         if (!noload) {
           __syncwarp();
-          fence_proxy_async();
+          if (LOADER == 0) fence_proxy_async();
           if (run_done + STAGES < total) issue(run_done + STAGES, s);
           if (cnt == 2 && run_done + 1 + STAGES < total) issue(run_done + 1 + STAGES, sB);
         }
@@ -621,7 +705,8 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
     }
   }
 
-  if (dead) {  // let the copies still in flight land before the shared memory is given back
+  if (LOADER == 1) cp_async_wait_group<0>();
+  if (LOADER == 0 && dead) {  // let the copies still in flight land before the shared memory is given back
     for (int g = n_done; g < n_issued; ++g) {
       const int st = g % STAGES;
       WaitBudget budget;
@@ -714,7 +799,7 @@ __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamP
 
 constexpr int64_t kPartialBytes = 4 * kHeadDim * 4 + 16 + 16 + 4;  // o, m, l of four heads and the header
 
-template <int NW, int STAGES>
+template <int NW, int STAGES, int LOADER>
 int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_seq_len, int sm_count,
                    cudaStream_t stream) {
   using R = Ring<NW, STAGES>;
@@ -738,7 +823,7 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   sp.ws_l = sp.ws_m + slots * 4;
   sp.ws_hdr = reinterpret_cast<int*>(sp.ws_l + slots * 4);
 
-  auto kern = p.stat_bf16 ? decode_stream_kernel<NW, STAGES, true> : decode_stream_kernel<NW, STAGES, false>;
+  auto kern = p.stat_bf16 ? decode_stream_kernel<NW, STAGES, true, LOADER> : decode_stream_kernel<NW, STAGES, false, LOADER>;
   static bool configured[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -788,9 +873,13 @@ int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, int 
   const int sms = device_sm_count();
   if (sms <= 0) return BKV_ERR_CUDA;
   switch (config) {
-    case 1: return launch_variant<8, 4>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 3: return launch_variant<16, 2>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    default: return launch_variant<12, 3>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 1: return launch_variant<8, 4, 0>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 2: return launch_variant<12, 3, 0>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 3: return launch_variant<16, 2, 0>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 5: return launch_variant<12, 3, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 6: return launch_variant<8, 4, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 7: return launch_variant<16, 2, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    default: return launch_variant<12, 3, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
   }
 }
 

@@ -67,6 +67,22 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uin
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+// 16-byte asynchronous copies (per thread, generic proxy), grouped per tile
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// returns when at most `pending` (0..3) of this thread's newest groups are still in flight
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+  if (pending <= 0) cp_async_wait_group<0>();
+  else if (pending == 1) cp_async_wait_group<1>();
+  else if (pending == 2) cp_async_wait_group<2>();
+  else cp_async_wait_group<3>();
+}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
