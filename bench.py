@@ -53,12 +53,19 @@ def parse_args():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0, help="0 = launch policy")
     ap.add_argument("--stat", default="fp16", choices=["fp16", "bf16"])
+    ap.add_argument("--experiment-hot-pages", type=int, default=0,
+                    help="diagnostic, not a benchmark: fold the block table onto this many physical pages so "
+                         "that the packed cache is read from L2; separates DRAM effects from the rest")
     ap.add_argument("--variant", type=int, default=0,
                     help="0 auto (persistent tensor-core schedule), 1 CUDA-core kernel, 20+ split-grid tensor-core "
                          "configurations, 40+ persistent configurations")
     ap.add_argument("--cpu-sample-requests", type=int, default=0, help="0 = one per host core")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--dense-baseline", action="store_true", help="also time the bf16-KV kernel on the same shapes")
+    ap.add_argument("--dense-baseline", action="store_true",
+                    help="also time bf16-KV decode attention on the same shapes: this library's plain kernel and, "
+                         "when importable, flash_attn's flash_attn_with_kvcache (library code, reported as such)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="context sweep 1K..128K at 4M KV tokens on one GPU, with the bf16-KV baselines")
     return ap.parse_args()
 
 
@@ -228,6 +235,35 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.sweep:
+        # context sweep at a constant 4M KV tokens (batch = 4M / context), one JSON line per point
+        points = [(4096, 1024), (1024, 4096), (256, 16384), (128, 32768), (64, 65536), (32, 131072)]
+    else:
+        points = [(args.batch, args.ctx)]
+    for batch, ctx in points:
+        point = argparse.Namespace(**vars(args))
+        point.batch, point.ctx = batch, ctx
+        if args.sweep:
+            point.steps, point.no_cpu_baseline, point.dense_baseline = min(args.steps, 200), True, True
+        line = measure(point, world, rank, local_rank, dev)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        torch.cuda.empty_cache()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def measure(args, world, rank, local_rank, dev):
+    """Build the packed cache for one (batch, context) point, time the decode step and the
+    end-to-end serving step; returns the JSON line (rank 0) or None."""
+    import torch
+    import torch.distributed as dist
+
+    from beyond_kv_cache_b200 import _lib, synth
+    from beyond_kv_cache_b200.quant.beyond_cute import PagedLayout, write_tokens_to_paged_cache
+    from beyond_kv_cache_b200.quant.fa4_cute import beyond_mixed_decode_runtime as rt
+
     B, ctx, BS = args.batch, args.ctx, args.page
     stat_dtype = torch.float16 if args.stat == "fp16" else torch.bfloat16
     layout = PagedLayout.build_hnd(BS, HEADS_KV, HEAD_DIM, 4, 32, 32)
@@ -259,8 +295,10 @@ def main():
     scale = synth.softmax_scale()
     streamed = (args.variant == 0 or args.variant >= 40) and "stream" in ws
 
+    bt_timed = block_table % args.experiment_hot_pages if args.experiment_hot_pages > 0 else block_table
+
     def decode_step():
-        rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=block_table,
+        rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=bt_timed,
                                  seq_lens=seq_lens, k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
                                  workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
 
@@ -377,6 +415,8 @@ def main():
             },
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            **({"experiment": f"block table folded onto {args.experiment_hot_pages} pages (L2-resident): not a "
+                              "bandwidth measurement"} if args.experiment_hot_pages > 0 else {}),
             "gpu_launches": args.steps * (2 if (streamed or spec.num_splits > 1) else 1),
             "clocks": clocks,
         }
@@ -385,10 +425,8 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_decode_baseline(args, args.cpu_sample_requests)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        return line
+    return None
 
 
 def time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, splits, scale, args):
@@ -420,7 +458,51 @@ def time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, splits, sc
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     nbytes = B * ctx * HEADS_KV * 512
-    return {"us_per_layer": ms * 1e3, "GBps_bf16_bytes": nbytes / (ms * 1e-3) / 1e9, "bytes_per_token_head": 512}
+    result = {"us_per_layer": ms * 1e3, "GBps_bf16_bytes": nbytes / (ms * 1e-3) / 1e9, "bytes_per_token_head": 512,
+              "kernel": "bkv_decode_dense_sm100 (this library, CUDA cores)"}
+    del k_pages, v_pages
+    result["library_flash_attn"] = time_flash_attn_library(torch, dev, B, ctx, q, scale, args.steps)
+    return result
+
+
+def time_flash_attn_library(torch, dev, B, ctx, q, scale, steps):
+    """flash_attn_with_kvcache on a paged bf16 cache of the same shape (library code, not part
+    of this product: the strongest bf16-KV decode kernel available in the image).  Its paged
+    mode needs 256-token pages."""
+    try:
+        from flash_attn import flash_attn_with_kvcache
+    except Exception as exc:
+        return {"unavailable": repr(exc)}
+    try:
+        page = 256
+        pages_per_seq = (ctx + page - 1) // page
+        num_pages = B * pages_per_seq
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(5)
+        bt = torch.randperm(num_pages, generator=gen, device=dev).to(torch.int32).view(B, pages_per_seq)
+        kc = torch.randn((num_pages, page, HEADS_KV, HEAD_DIM), device=dev).to(torch.bfloat16)
+        vc = torch.randn((num_pages, page, HEADS_KV, HEAD_DIM), device=dev).to(torch.bfloat16)
+        lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        q4 = q.view(B, 1, HEADS_Q, HEAD_DIM)
+
+        def step():
+            return flash_attn_with_kvcache(q4, kc, vc, cache_seqlens=lens, block_table=bt, softmax_scale=scale)
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        nbytes = B * ctx * HEADS_KV * 512
+        return {"us_per_layer": ms * 1e3, "GBps_bf16_bytes": nbytes / (ms * 1e-3) / 1e9, "page_tokens": page,
+                "kernel": "flash_attn.flash_attn_with_kvcache"}
+    except Exception as exc:
+        return {"unavailable": repr(exc)}
 
 
 if __name__ == "__main__":

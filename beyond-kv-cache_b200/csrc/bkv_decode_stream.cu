@@ -37,7 +37,8 @@ namespace {
 
 using namespace mma;
 
-constexpr int kMaxBatch = 1024;
+constexpr int kMaxBatch = 1024;        // the per-request tile counts of larger batches do not fit in shared memory:
+constexpr int kMaxBatchPlanned = 16384;  // a one-CTA kernel then leaves their prefix sums in the workspace
 constexpr int kMaxPagesLog2 = 26;  // a page id and the tile's position in its page share one word
 // ring slot of this kernel: the tile format plus a 16-byte gap in front of the V statistics of
 // groups 2 and 3, which keeps the statistic loads of a half-warp (two groups at once) conflict-free
@@ -60,6 +61,7 @@ struct StreamParams {
   float* ws_m;   // [slots][4]  log2 domain
   float* ws_l;   // [slots][4]
   int* ws_hdr;   // [slots]  (virtual head * batch + request) * 2 + (1: last part), or kHdrNone
+  int* ws_prefix;  // [batch + 1] tiles before request b, written by stream_prefix_kernel when batch > kMaxBatch
   int quads;     // query-head quads per kv head
 };
 
@@ -127,7 +129,7 @@ struct Ring {
 // LOADER 0: bulk copies (cp.async.bulk) completing on one mbarrier per ring stage, issued by an
 // elected lane.  LOADER 1: every lane moves 16-byte pieces with cp.async, one commit group per
 // tile; the pieces land wherever the tile format wants them, at a fifth of the instructions.
-template <int NW, int STAGES, bool STAT_BF16, int LOADER>
+template <int NW, int STAGES, bool STAT_BF16, int LOADER, int PAIR = 2>
 __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamParams sp) {
   static_assert(STAGES <= 4, "cp_async_wait_pending handles up to three groups in flight");
   using R = Ring<NW, STAGES>;
@@ -156,6 +158,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
   const bool noload = (p.flags & BKV_FLAG_DEBUG_NOLOAD) != 0;
 
   if (p.flags & BKV_FLAG_PDL_WAIT) pdl_wait();
+  pdl_launch_dependents();  // the fix-up grid may be set up now; it waits for this grid to finish
 
   if (tid == 0) {
     for (int i = 0; i < NW * STAGES; ++i) mbar_init(kFullBar + 8 * i, 1);
@@ -163,8 +166,10 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
   }
 
   // ---- tiles before every request (exclusive prefix sum over the batch) ------------------
-  int* prefix = reinterpret_cast<int*>(gptr(kPrefixAddr));
-  {
+  const bool planned = B > kMaxBatch;
+  const int* const prefix = planned ? sp.ws_prefix : reinterpret_cast<const int*>(gptr(kPrefixAddr));
+  if (!planned) {
+    int* const prefix = reinterpret_cast<int*>(gptr(kPrefixAddr));
     int* tot = reinterpret_cast<int*>(gptr(kChunkTot));
     const int nchunks = (B + 31) >> 5;
     for (int c = warp; c < nchunks; c += NW) {
@@ -279,37 +284,11 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
     const int hq0 = head * gqa + quad * 4;
     const int nh = min(4, gqa - quad * 4);
 
-    __syncthreads();  // the previous head's tables are no longer read
-    {                 // level tables -> fp16 in shared memory
-      __half* lv = reinterpret_cast<__half*>(gptr(kLevels));
-      for (int i = tid; i < 128; i += NW * 32) {
-        const int which = i >> 6, g = (i >> 4) & 3, c = i & 15;
-        lv[i] = __float2half_rn(which ? load_v_level(p, head, g, c) : load_k_level(p, head, g, c));
-      }
-    }
-    __syncthreads();
-    {  // byte -> (level[low nibble], level[high nibble]) tables, one copy per bank.
-       // Block P (P = 0, 1) holds, in bank l, the K table of group 2*((l>>1)&1)+P and the
-       // V table of group 2*(l>>4)+P: the groups lane l needs when an MMA works on pair P.
-      const unsigned short* lv = reinterpret_cast<const unsigned short*>(gptr(kLevels));
-      for (int e = warp; e < 512; e += NW) {
-        const int P = e >> 8, byte = e & 255;
-        const int kg = 2 * ((lane >> 1) & 1) + P, vg = 2 * (lane >> 4) + P;
-        const uint32_t kval = lv[kg * 16 + (byte & 15)] | (static_cast<uint32_t>(lv[kg * 16 + (byte >> 4)]) << 16);
-        const uint32_t vval = lv[64 + vg * 16 + (byte & 15)] | (static_cast<uint32_t>(lv[64 + vg * 16 + (byte >> 4)]) << 16);
-        uint32_t* row = reinterpret_cast<uint32_t*>(gptr(kLutAddr + P * kLutBlock + byte * 256));
-        row[lane] = kval;
-        row[32 + lane] = vval;
-      }
-    }
-    __syncthreads();
-    if (dead) continue;
-
     // ---- this warp's run of tiles [wa, wb) inside the head ---------------------------------
     const int wa = first + static_cast<int>(static_cast<int64_t>(span) * warp / NW);
     const int wb = first + static_cast<int>(static_cast<int64_t>(span) * (warp + 1) / NW);
     const int total = wb - wa;
-    if (total <= 0) continue;
+    const bool work = total > 0 && !dead;
 
     // loader: one lane issues the bulk copies of a tile, so every operand is warp-uniform.
     // Chunks: K codes of tokens 0-7 / 8-15 (512 B each), K statistics (256), V codes (512
@@ -394,13 +373,39 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
       }
       ++n_issued;
     };
-    if (!noload || n_issued == 0) {
+    if (work && (!noload || n_issued == 0)) {  // first ring fill: in flight while the tables are built
       int st = s;
       for (int j = 0; j < min(total, STAGES); ++j) {
         issue(j, st);
         st = st + 1 == STAGES ? 0 : st + 1;
       }
     }
+
+    __syncthreads();  // the previous head's tables are no longer read
+    {                 // level tables -> fp16 in shared memory
+      __half* lv = reinterpret_cast<__half*>(gptr(kLevels));
+      for (int i = tid; i < 128; i += NW * 32) {
+        const int which = i >> 6, g = (i >> 4) & 3, c = i & 15;
+        lv[i] = __float2half_rn(which ? load_v_level(p, head, g, c) : load_k_level(p, head, g, c));
+      }
+    }
+    __syncthreads();
+    {  // byte -> (level[low nibble], level[high nibble]) tables, one copy per bank.
+       // Block P (P = 0, 1) holds, in bank l, the K table of group 2*((l>>1)&1)+P and the
+       // V table of group 2*(l>>4)+P: the groups lane l needs when an MMA works on pair P.
+      const unsigned short* lv = reinterpret_cast<const unsigned short*>(gptr(kLevels));
+      for (int e = warp; e < 512; e += NW) {
+        const int P = e >> 8, byte = e & 255;
+        const int kg = 2 * ((lane >> 1) & 1) + P, vg = 2 * (lane >> 4) + P;
+        const uint32_t kval = lv[kg * 16 + (byte & 15)] | (static_cast<uint32_t>(lv[kg * 16 + (byte >> 4)]) << 16);
+        const uint32_t vval = lv[64 + vg * 16 + (byte & 15)] | (static_cast<uint32_t>(lv[64 + vg * 16 + (byte >> 4)]) << 16);
+        uint32_t* row = reinterpret_cast<uint32_t*>(gptr(kLutAddr + P * kLutBlock + byte * 256));
+        row[lane] = kval;
+        row[32 + lane] = vval;
+      }
+    }
+    __syncthreads();
+    if (!work) continue;
 
     // ---- attention state of the request being streamed ------------------------------------
     uint32_t qb[2][4][2];  // B operand of QK: q of head hcol, pre-scaled by softmax_scale * log2(e)
@@ -611,7 +616,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
       l_run = 0.f;
 
       for (int k = k0; k < kend;) {
-        const int cnt = min(2, kend - k);
+        const int cnt = min(PAIR, kend - k);
         const int sB = s + 1 == STAGES ? 0 : s + 1;
         const uint32_t phaseB = s + 1 == STAGES ? phase ^ 1u : phase;
         // (the timing experiment stops issuing after the first fill and so stops waiting too)
@@ -717,24 +722,27 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
 }
 
 // ---- fix-up: merge the chains of partials of the requests that were cut ---------------------
-// One CTA per (range, query head of the quad); it owns the request whose FIRST part is slot 1
-// of its range and walks the following ranges' slot 0 until the part flagged last.
-constexpr int kFixThreads = 128;
+// One CTA per range, 128 threads per query head of the quad; it owns the request whose FIRST
+// part is slot 1 of its range and walks the following ranges' slot 0 until the part flagged
+// last.  Most CTAs find nothing to own and leave after one load.
+constexpr int kFixThreads = 4 * kHeadDim;
+constexpr int kFixWindow = 128;
 constexpr int kFixBatch = 8;
 
 __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamParams sp, const int num_ranges) {
   const DecodeParams& p = sp.d;
-  const int range = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  pdl_wait();  // launched while the decode grid still runs: its writes are visible from here on
+  const int range = blockIdx.x, h = threadIdx.x >> 7, d = threadIdx.x & (kHeadDim - 1);
   const int hd = sp.ws_hdr[2 * range + 1];
   if (hd < 0) return;
   const int item = hd >> 1;
   const int vh = item / p.batch, b = item - vh * p.batch;
   const int head = vh / sp.quads, quad = vh - head * sp.quads;
   const int gqa = p.heads_q / p.heads_kv;
-  if (h >= min(4, gqa - quad * 4)) return;
+  const bool live = h < min(4, gqa - quad * 4);
 
-  __shared__ int s_hdr[kFixThreads];
-  __shared__ int s_list[kFixThreads];
+  __shared__ int s_hdr[kFixWindow];
+  __shared__ int s_list[kFixWindow];
   __shared__ int s_cnt, s_done;
 
   float M = -CUDART_INF_F, num = 0.f, den = 0.f;
@@ -747,20 +755,22 @@ __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamP
     den = den * a + l2 * w;
     M = Mn;
   };
-  {
+  if (live) {
     const int64_t row = static_cast<int64_t>(2 * range + 1) * 4 + h;
     merge(sp.ws_m[row], sp.ws_l[row], sp.ws_o[row * kHeadDim + d]);
   }
   const bool chain_open = (hd & 1) == 0;
-  for (int base = range + 1; chain_open && base < num_ranges; base += kFixThreads) {
-    const int r = base + d;
-    s_hdr[d] = r < num_ranges ? sp.ws_hdr[2 * r] : kHdrNone;
+  for (int base = range + 1; chain_open && base < num_ranges; base += kFixWindow) {
+    if (threadIdx.x < kFixWindow) {
+      const int r = base + threadIdx.x;
+      s_hdr[threadIdx.x] = r < num_ranges ? sp.ws_hdr[2 * r] : kHdrNone;
+    }
     __syncthreads();
-    if (d == 0) {
-      int cnt = 0, done = base + kFixThreads >= num_ranges ? 1 : 0;
-      for (int j = 0; j < kFixThreads; ++j) {
+    if (threadIdx.x == 0) {
+      int cnt = 0, done = base + kFixWindow >= num_ranges ? 1 : 0;
+      for (int j = 0; j < kFixWindow; ++j) {
         const int hj = s_hdr[j];
-        if (hj < 0) continue;            // an empty range
+        if (hj < 0) continue;                        // an empty range
         if ((hj >> 1) != item) { done = 1; break; }  // cannot happen: the chain is contiguous
         s_list[cnt++] = base + j;
         if (hj & 1) { done = 1; break; }
@@ -770,36 +780,84 @@ __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamP
     }
     __syncthreads();
     const int cnt = s_cnt;
-    for (int c0 = 0; c0 < cnt; c0 += kFixBatch) {
-      float m2[kFixBatch], l2[kFixBatch], o2[kFixBatch];
+    if (live) {
+      for (int c0 = 0; c0 < cnt; c0 += kFixBatch) {
+        float m2[kFixBatch], l2[kFixBatch], o2[kFixBatch];
 #pragma unroll
-      for (int u = 0; u < kFixBatch; ++u) {
-        l2[u] = 0.f;
-        m2[u] = 0.f;
-        o2[u] = 0.f;
-        if (c0 + u < cnt) {
-          const int64_t row = static_cast<int64_t>(2 * s_list[c0 + u]) * 4 + h;
-          m2[u] = sp.ws_m[row];
-          l2[u] = sp.ws_l[row];
-          o2[u] = sp.ws_o[row * kHeadDim + d];
+        for (int u = 0; u < kFixBatch; ++u) {
+          l2[u] = 0.f;
+          m2[u] = 0.f;
+          o2[u] = 0.f;
+          if (c0 + u < cnt) {
+            const int64_t row = static_cast<int64_t>(2 * s_list[c0 + u]) * 4 + h;
+            m2[u] = sp.ws_m[row];
+            l2[u] = sp.ws_l[row];
+            o2[u] = sp.ws_o[row * kHeadDim + d];
+          }
         }
-      }
 #pragma unroll
-      for (int u = 0; u < kFixBatch; ++u) merge(m2[u], l2[u], o2[u]);
+        for (int u = 0; u < kFixBatch; ++u) merge(m2[u], l2[u], o2[u]);
+      }
     }
     const int done = s_done;
     __syncthreads();
     if (done) break;
   }
+  if (!live) return;
   const float o = den > 0.f ? num / den : 0.f;
   const int64_t row = static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4 + h;
   store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
   if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
 }
 
-constexpr int64_t kPartialBytes = 4 * kHeadDim * 4 + 16 + 16 + 4;  // o, m, l of four heads and the header
+// tiles before every request for batches beyond kMaxBatch (one CTA, inclusive scan by chunks)
+__global__ void __launch_bounds__(1024) stream_prefix_kernel(const DecodeParams p, int* __restrict__ prefix) {
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lo = max(p.token_lo, 0);
+  if (tid == 0) {
+    s_carry = 0;
+    prefix[0] = 0;
+  }
+  __syncthreads();
+  for (int base = 0; base < p.batch; base += 1024) {
+    const int b = base + tid;
+    int n = 0;
+    if (b < p.batch) {
+      const int hi_b = min(p.token_hi, p.seq_lens[b]);
+      n = hi_b > lo ? (hi_b - lo + kTile - 1) / kTile : 0;
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, n, o);
+      if (lane >= o) n += y;
+    }
+    if (lane == 31) s_warp[warp] = n;
+    __syncthreads();
+    if (warp == 0) {
+      const int v = s_warp[lane];
+      int w = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      s_warp[lane] = w - v;
+    }
+    __syncthreads();
+    const int incl = s_carry + s_warp[warp] + n;
+    if (b < p.batch) prefix[1 + b] = incl;
+    __syncthreads();
+    if (tid == 1023) s_carry = incl;
+    __syncthreads();
+  }
+}
 
-template <int NW, int STAGES, int LOADER>
+constexpr int64_t kPartialBytes = 4 * kHeadDim * 4 + 16 + 16 + 4;  // o, m, l of four heads and the header
+constexpr int64_t kPlannedPrefixBytes = (kMaxBatchPlanned + 64) * 4;  // a multiple of 256
+
+template <int NW, int STAGES, int LOADER, int PAIR = 2>
 int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_seq_len, int sm_count,
                    cudaStream_t stream) {
   using R = Ring<NW, STAGES>;
@@ -816,14 +874,21 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   const int C = static_cast<int>(ctas);
   const int num_ranges = C * 2 * NW;
   const int64_t slots = 2ll * num_ranges;
-  if (!ws || ws_bytes < slots * kPartialBytes) return BKV_ERR_ARG;
-  char* w = static_cast<char*>(ws);
+  if (!ws || ws_bytes < slots * kPartialBytes + kPlannedPrefixBytes) return BKV_ERR_ARG;
+  char* w = static_cast<char*>(ws) + kPlannedPrefixBytes;  // the prefix sums come first
   sp.ws_o = reinterpret_cast<float*>(w);
   sp.ws_m = reinterpret_cast<float*>(w + slots * (4 * kHeadDim * 4));
   sp.ws_l = sp.ws_m + slots * 4;
   sp.ws_hdr = reinterpret_cast<int*>(sp.ws_l + slots * 4);
+  sp.ws_prefix = static_cast<int*>(ws);
+  if (p.batch > kMaxBatch) {
+    stream_prefix_kernel<<<1, 1024, 0, stream>>>(p, sp.ws_prefix);
+    const int rcp = check_launch("bkv_decode_stream_sm100(prefix)");
+    if (rcp != BKV_OK) return rcp;
+  }
 
-  auto kern = p.stat_bf16 ? decode_stream_kernel<NW, STAGES, true, LOADER> : decode_stream_kernel<NW, STAGES, false, LOADER>;
+  auto kern = p.stat_bf16 ? decode_stream_kernel<NW, STAGES, true, LOADER, PAIR>
+                          : decode_stream_kernel<NW, STAGES, false, LOADER, PAIR>;
   static bool configured[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -841,8 +906,23 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp);
   int rc = check_launch("bkv_decode_stream_sm100(decode)");
   if (rc != BKV_OK) return rc;
-  stream_fixup_kernel<<<dim3(num_ranges, 4), kFixThreads, 0, stream>>>(sp, num_ranges);
-  return check_launch("bkv_decode_stream_sm100(fixup)");
+  // programmatic dependent launch: the fix-up grid is set up while the decode grid drains
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_ranges);
+  cfg.blockDim = dim3(kFixThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, stream_fixup_kernel, sp, num_ranges);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "bkv_decode_stream_sm100(fixup)");
+    return BKV_ERR_CUDA;
+  }
+  return BKV_OK;
 }
 
 int device_sm_count() {
@@ -860,7 +940,8 @@ int device_sm_count() {
 
 int64_t stream_workspace_bytes() {
   const int64_t sms = device_sm_count();
-  return sms * 2 * 16 * 2 * kPartialBytes;  // ranges of the widest configuration (16 warps), two slots each
+  // the prefix sums, then the ranges of the widest configuration (16 warps), two slots each
+  return kPlannedPrefixBytes + sms * 2 * 16 * 2 * kPartialBytes;
 }
 
 int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_seq_len, cudaStream_t stream,
@@ -869,7 +950,7 @@ int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, int 
   if (p.block_size % kTile != 0 || (r & (r - 1)) != 0 || p.block_size > 1024) return BKV_ERR_UNSUPPORTED;
   if ((p.page_stride * 4) % 16 != 0 || !aligned16(p.cache)) return BKV_ERR_UNSUPPORTED;
   if (p.token_lo % p.block_size != 0) return BKV_ERR_UNSUPPORTED;
-  if (p.batch > kMaxBatch || p.num_pages > (1ll << kMaxPagesLog2)) return BKV_ERR_UNSUPPORTED;
+  if (p.batch > kMaxBatchPlanned || p.num_pages > (1ll << kMaxPagesLog2)) return BKV_ERR_UNSUPPORTED;
   const int sms = device_sm_count();
   if (sms <= 0) return BKV_ERR_CUDA;
   switch (config) {
@@ -879,6 +960,9 @@ int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, int 
     case 5: return launch_variant<12, 3, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
     case 6: return launch_variant<8, 4, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
     case 7: return launch_variant<16, 2, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 8: return launch_variant<9, 4, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 9: return launch_variant<12, 3, 1, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 10: return launch_variant<16, 2, 1, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
     default: return launch_variant<12, 3, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
   }
 }

@@ -257,9 +257,9 @@ def allocate_runtime_workspace(spec: DecodeRuntimeSpec, *, device: torch.device)
 
 
 def stream_schedule_supported(spec: DecodeRuntimeSpec) -> bool:
-    """The persistent schedule (``bkv_decode_stream_sm100``) keeps a per-request table in
-    shared memory and packs page ids into 26 bits; larger buckets use the split grid."""
-    return spec.batch_size <= 1024 and spec.physical_pages <= (1 << 26)
+    """The persistent schedule (``bkv_decode_stream_sm100``) plans at most 16384 requests
+    per launch and packs page ids into 26 bits; larger buckets use the split grid."""
+    return spec.batch_size <= 16384 and spec.physical_pages <= (1 << 26)
 
 
 def _validate_launch_tensors(*, spec, q, out, block_table, seq_lens, k_qpoints_lane_major, v_qpoints_code_major, workspace) -> None:

@@ -125,7 +125,7 @@ int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const v
  * bkv_decode_stream_workspace_bytes() bytes (the bound depends on the current device
  * only, not on the shapes); contents need not be initialised and are overwritten.
  * Two calls that may overlap on the GPU need separate workspaces.
- * Returns BKV_ERR_UNSUPPORTED (launch nothing) for batch > 1024, more than 2^26 pages or
+ * Returns BKV_ERR_UNSUPPORTED (launch nothing) for batch > 16384, more than 2^26 pages or
  * a page size the tensor-core kernel does not handle; use bkv_decode_sm100 then.
  * variant: 0 default configuration; 41 / 43 select 8 / 16 warps per CTA.
  */
