@@ -54,6 +54,8 @@ constexpr uint32_t kLevels = kSmemBase + 1280;    // fp16 [K|V][4][16]
 constexpr int kHdrNone = -1;
 
 constexpr int BKV_FLAG_DEBUG_NOLOAD = 0x100;  // timing experiment: reuse the first ring fill
+constexpr int BKV_FLAG_DEBUG_EQUAL_SHARES = 0x800;     // experiment: force equal shares
+constexpr int BKV_FLAG_DEBUG_ALIGNED_SHARES = 0x1000;  // experiment: force head-aligned shares
 
 struct StreamParams {
   DecodeParams d;
@@ -63,6 +65,7 @@ struct StreamParams {
   int* ws_hdr;   // [slots]  (virtual head * batch + request) * 2 + (1: last part), or kHdrNone
   int* ws_prefix;  // [batch + 1] tiles before request b, written by stream_prefix_kernel when batch > kMaxBatch
   int quads;     // query-head quads per kv head
+  int aligned;   // 1: every CTA's share lies inside one head (heads get floor or ceil of C / heads CTAs)
 };
 
 // All bulk copies of one tile, issued by one elected lane of a converged warp in a single
@@ -214,7 +217,29 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
     }
   }
   const int64_t G = static_cast<int64_t>(p.heads_kv * quads) * Tb;
-  const int64_t ga = G * cta / C, gb = G * (cta + 1) / C;
+  int64_t ga, gb;  // this CTA's share of the line
+  if (sp.aligned) {
+    // heads 0..extra-1 are served by base+1 CTAs, the others by base; no share straddles two
+    // heads, so the tables are built once, at the price of unequal shares
+    const int hv = p.heads_kv * quads;
+    const int base = C / hv, extra = C - base * hv;
+    int h, idx, cnt;
+    if (cta < extra * (base + 1)) {
+      h = cta / (base + 1);
+      idx = cta - h * (base + 1);
+      cnt = base + 1;
+    } else {
+      const int c2 = cta - extra * (base + 1);
+      h = extra + c2 / base;
+      idx = c2 - (c2 / base) * base;
+      cnt = base;
+    }
+    ga = static_cast<int64_t>(h) * Tb + static_cast<int64_t>(Tb) * idx / cnt;
+    gb = static_cast<int64_t>(h) * Tb + static_cast<int64_t>(Tb) * (idx + 1) / cnt;
+  } else {
+    ga = G * cta / C;
+    gb = G * (cta + 1) / C;
+  }
 
   // ---- per-lane roles (see the file comment) ----------------------------------------------
   const int ksel = tig >> 1, khalf = tig & 1;     // QK: this lane's k-slots carry half khalf of group 2*ksel+P
@@ -394,6 +419,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
        // Block P (P = 0, 1) holds, in bank l, the K table of group 2*((l>>1)&1)+P and the
        // V table of group 2*(l>>4)+P: the groups lane l needs when an MMA works on pair P.
       const unsigned short* lv = reinterpret_cast<const unsigned short*>(gptr(kLevels));
+#pragma unroll 4
       for (int e = warp; e < 512; e += NW) {
         const int P = e >> 8, byte = e & 255;
         const int kg = 2 * ((lane >> 1) & 1) + P, vg = 2 * (lane >> 4) + P;
@@ -722,92 +748,117 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
 }
 
 // ---- fix-up: merge the chains of partials of the requests that were cut ---------------------
-// One CTA per range, 128 threads per query head of the quad; it owns the request whose FIRST
-// part is slot 1 of its range and walks the following ranges' slot 0 until the part flagged
-// last.  Most CTAs find nothing to own and leave after one load.
-constexpr int kFixThreads = 4 * kHeadDim;
-constexpr int kFixWindow = 128;
-constexpr int kFixBatch = 8;
+// One CTA per decode CTA looks at the 2*NW ranges of that CTA.  A range OWNS the request whose
+// first part is its slot 1; the chain continues through slot 0 of the following ranges up to
+// the part flagged last.  The four 128-thread groups of the CTA each take one owner at a time
+// (thread = output dimension, the four query heads in registers).
+constexpr int kFixThreads = 512;
+constexpr int kFixGroup = 128;
+constexpr int kFixBatch = 4;
 
-__global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamParams sp, const int num_ranges) {
+__device__ __forceinline__ void group_sync(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kFixGroup) : "memory");
+}
+
+__global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamParams sp, const int ranges_per_cta,
+                                                                  const int num_ranges) {
   const DecodeParams& p = sp.d;
   pdl_wait();  // launched while the decode grid still runs: its writes are visible from here on
-  const int range = blockIdx.x, h = threadIdx.x >> 7, d = threadIdx.x & (kHeadDim - 1);
-  const int hd = sp.ws_hdr[2 * range + 1];
-  if (hd < 0) return;
-  const int item = hd >> 1;
-  const int vh = item / p.batch, b = item - vh * p.batch;
-  const int head = vh / sp.quads, quad = vh - head * sp.quads;
-  const int gqa = p.heads_q / p.heads_kv;
-  const bool live = h < min(4, gqa - quad * 4);
-
-  __shared__ int s_hdr[kFixWindow];
-  __shared__ int s_list[kFixWindow];
-  __shared__ int s_cnt, s_done;
-
-  float M = -CUDART_INF_F, num = 0.f, den = 0.f;
-  auto merge = [&](float m2, float l2, float o2) {
-    if (!(l2 > 0.f)) return;
-    const float Mn = fmaxf(M, m2);
-    const float a = (M == -CUDART_INF_F) ? 0.f : exp2f(M - Mn);
-    const float w = exp2f(m2 - Mn);
-    num = num * a + o2 * w;
-    den = den * a + l2 * w;
-    M = Mn;
-  };
-  if (live) {
-    const int64_t row = static_cast<int64_t>(2 * range + 1) * 4 + h;
-    merge(sp.ws_m[row], sp.ws_l[row], sp.ws_o[row * kHeadDim + d]);
+  __shared__ int s_owner[32];
+  __shared__ int s_nown;
+  __shared__ int s_hdr[4][kFixGroup];
+  __shared__ int s_list[4][kFixGroup];
+  __shared__ int s_cnt[4], s_done[4];
+  const int tid = threadIdx.x, g = tid >> 7, d = tid & (kFixGroup - 1);
+  const int r0 = blockIdx.x * ranges_per_cta;
+  if (tid < 32) {  // ranges_per_cta <= 32
+    const int hd = tid < ranges_per_cta ? sp.ws_hdr[2 * (r0 + tid) + 1] : kHdrNone;
+    const unsigned mask = __ballot_sync(0xffffffffu, hd >= 0);
+    if (hd >= 0) s_owner[__popc(mask & ((1u << tid) - 1))] = r0 + tid;
+    if (tid == 0) s_nown = __popc(mask);
   }
-  const bool chain_open = (hd & 1) == 0;
-  for (int base = range + 1; chain_open && base < num_ranges; base += kFixWindow) {
-    if (threadIdx.x < kFixWindow) {
-      const int r = base + threadIdx.x;
-      s_hdr[threadIdx.x] = r < num_ranges ? sp.ws_hdr[2 * r] : kHdrNone;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int cnt = 0, done = base + kFixWindow >= num_ranges ? 1 : 0;
-      for (int j = 0; j < kFixWindow; ++j) {
-        const int hj = s_hdr[j];
-        if (hj < 0) continue;                        // an empty range
-        if ((hj >> 1) != item) { done = 1; break; }  // cannot happen: the chain is contiguous
-        s_list[cnt++] = base + j;
-        if (hj & 1) { done = 1; break; }
-      }
-      s_cnt = cnt;
-      s_done = done;
-    }
-    __syncthreads();
-    const int cnt = s_cnt;
-    if (live) {
-      for (int c0 = 0; c0 < cnt; c0 += kFixBatch) {
-        float m2[kFixBatch], l2[kFixBatch], o2[kFixBatch];
+  __syncthreads();
+  const int nown = s_nown;
+  const int gqa = p.heads_q / p.heads_kv;
+  for (int oi = g; oi < nown; oi += 4) {
+    const int range = s_owner[oi];
+    const int hd = sp.ws_hdr[2 * range + 1];
+    const int item = hd >> 1;
+    const int vh = item / p.batch, b = item - vh * p.batch;
+    const int head = vh / sp.quads, quad = vh - head * sp.quads;
+    const int nh = min(4, gqa - quad * 4);
+    float M[4], num[4], den[4];
 #pragma unroll
-        for (int u = 0; u < kFixBatch; ++u) {
-          l2[u] = 0.f;
-          m2[u] = 0.f;
-          o2[u] = 0.f;
-          if (c0 + u < cnt) {
-            const int64_t row = static_cast<int64_t>(2 * s_list[c0 + u]) * 4 + h;
-            m2[u] = sp.ws_m[row];
-            l2[u] = sp.ws_l[row];
-            o2[u] = sp.ws_o[row * kHeadDim + d];
-          }
+    for (int h = 0; h < 4; ++h) {
+      M[h] = -CUDART_INF_F;
+      num[h] = 0.f;
+      den[h] = 0.f;
+    }
+    auto merge = [&](int h, float m2, float l2, float o2) {
+      if (!(l2 > 0.f)) return;
+      const float Mn = fmaxf(M[h], m2);
+      const float a = (M[h] == -CUDART_INF_F) ? 0.f : exp2f(M[h] - Mn);
+      const float w = exp2f(m2 - Mn);
+      num[h] = num[h] * a + o2 * w;
+      den[h] = den[h] * a + l2 * w;
+      M[h] = Mn;
+    };
+    auto merge_slot = [&](const int64_t slot0, const int64_t slot1, const int64_t slot2, const int64_t slot3, int n) {
+      const int64_t slots[kFixBatch] = {slot0, slot1, slot2, slot3};
+      float m2[kFixBatch][4], l2[kFixBatch][4], o2[kFixBatch][4];
+#pragma unroll
+      for (int u = 0; u < kFixBatch; ++u)
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const bool on = u < n && h < nh;
+          const int64_t row = slots[u] * 4 + h;
+          m2[u][h] = on ? sp.ws_m[row] : 0.f;
+          l2[u][h] = on ? sp.ws_l[row] : 0.f;
+          o2[u][h] = on ? sp.ws_o[row * kHeadDim + d] : 0.f;
         }
 #pragma unroll
-        for (int u = 0; u < kFixBatch; ++u) merge(m2[u], l2[u], o2[u]);
+      for (int u = 0; u < kFixBatch; ++u)
+#pragma unroll
+        for (int h = 0; h < 4; ++h) merge(h, m2[u][h], l2[u][h], o2[u][h]);
+    };
+    merge_slot(2ll * range + 1, 0, 0, 0, 1);
+    const bool chain_open = (hd & 1) == 0;
+    for (int base = range + 1; chain_open && base < num_ranges; base += kFixGroup) {
+      const int r = base + d;
+      s_hdr[g][d] = r < num_ranges ? sp.ws_hdr[2 * r] : kHdrNone;
+      group_sync(g);
+      if (d == 0) {
+        int cnt = 0, done = base + kFixGroup >= num_ranges ? 1 : 0;
+        for (int j = 0; j < kFixGroup; ++j) {
+          const int hj = s_hdr[g][j];
+          if (hj < 0) continue;                        // an empty range
+          if ((hj >> 1) != item) { done = 1; break; }  // cannot happen: the chain is contiguous
+          s_list[g][cnt++] = base + j;
+          if (hj & 1) { done = 1; break; }
+        }
+        s_cnt[g] = cnt;
+        s_done[g] = done;
       }
+      group_sync(g);
+      const int cnt = s_cnt[g];
+      for (int c0 = 0; c0 < cnt; c0 += kFixBatch) {
+        const int n = min(kFixBatch, cnt - c0);
+        merge_slot(2ll * s_list[g][c0], 2ll * s_list[g][min(c0 + 1, cnt - 1)], 2ll * s_list[g][min(c0 + 2, cnt - 1)],
+                   2ll * s_list[g][min(c0 + 3, cnt - 1)], n);
+      }
+      const int done = s_done[g];
+      group_sync(g);
+      if (done) break;
     }
-    const int done = s_done;
-    __syncthreads();
-    if (done) break;
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      if (h >= nh) continue;
+      const float o = den[h] > 0.f ? num[h] / den[h] : 0.f;
+      const int64_t row = static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4 + h;
+      store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
+      if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
+    }
   }
-  if (!live) return;
-  const float o = den > 0.f ? num / den : 0.f;
-  const int64_t row = static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4 + h;
-  store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
-  if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
 }
 
 // tiles before every request for batches beyond kMaxBatch (one CTA, inclusive scan by chunks)
@@ -872,6 +923,18 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   if (ctas < hv) ctas = hv;  // a share never spans more than two heads
   if (ctas > sm_count) ctas = sm_count;
   const int C = static_cast<int>(ctas);
+  // Equal shares make the CTAs whose share straddles two heads build the tables twice and
+  // restart their pipelines (about 10 us on the critical path); head-aligned shares avoid that
+  // but the heads served by fewer CTAs finish later.  Take the cheaper of the two estimates
+  // (0.1 us per tile and SM).
+  {
+    const int base = C / hv;
+    const double per_cta_us = static_cast<double>(tiles_max) / C * 0.1;
+    const double aligned_loss_us = per_cta_us * (static_cast<double>(C) / hv / base - 1.0);
+    sp.aligned = (C % hv == 0 || aligned_loss_us < 10.0) ? 1 : 0;
+    if (p.flags & BKV_FLAG_DEBUG_EQUAL_SHARES) sp.aligned = 0;
+    if (p.flags & BKV_FLAG_DEBUG_ALIGNED_SHARES) sp.aligned = 1;
+  }
   const int num_ranges = C * 2 * NW;
   const int64_t slots = 2ll * num_ranges;
   if (!ws || ws_bytes < slots * kPartialBytes + kPlannedPrefixBytes) return BKV_ERR_ARG;
@@ -908,7 +971,7 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   if (rc != BKV_OK) return rc;
   // programmatic dependent launch: the fix-up grid is set up while the decode grid drains
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(num_ranges);
+  cfg.gridDim = dim3(C);
   cfg.blockDim = dim3(kFixThreads);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
@@ -917,7 +980,7 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, stream_fixup_kernel, sp, num_ranges);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, stream_fixup_kernel, sp, 2 * NW, num_ranges);
   if (e != cudaSuccess) {
     set_last_cuda_error(e, "bkv_decode_stream_sm100(fixup)");
     return BKV_ERR_CUDA;
