@@ -26,6 +26,10 @@
 
 #include <type_traits>
 
+#include <cuda.h>
+
+#include <mutex>
+
 #include "bkv_decode_common.cuh"
 #include "bkv_mma_ptx.cuh"
 
@@ -40,11 +44,19 @@ using namespace mma;
 constexpr int kMaxBatch = 1024;        // the per-request tile counts of larger batches do not fit in shared memory:
 constexpr int kMaxBatchPlanned = 16384;  // a one-CTA kernel then leaves their prefix sums in the workspace
 constexpr int kMaxPagesLog2 = 26;  // a page id and the tile's position in its page share one word
-// ring slot of this kernel: the tile format plus a 16-byte gap in front of the V statistics of
-// groups 2 and 3, which keeps the statistic loads of a half-warp (two groups at once) conflict-free
-constexpr int kVStatSkew = 16;
-constexpr int kSlotBytes = kTileBytes + kVStatSkew;  // 2608
-constexpr uint32_t kRingLoS = kSmemBase + 1920;       // barriers, scan scratch and level tables end at 1536
+// Ring slot of this kernel: K codes, V codes (16 tokens x 64 B each), K statistics (16 tokens x
+// 16 B), V statistics (4 groups x 16 tokens x 4 B), all as 64-byte rows.  Inside the slot the
+// 16-byte chunk at byte offset o is stored at o ^ (((o >> 7) & 3) << 4): the 64-byte swizzle of
+// the tensor copy unit, which the cp.async loader reproduces.  It makes every per-lane load of the
+// MMA layouts conflict-free without padding, so one tensor copy moves one part of a tile.
+constexpr int kSwKCode = 0;
+constexpr int kSwVCode = 1024;
+constexpr int kSwKStat = 2048;
+constexpr int kSwVStat = 2304;
+constexpr int kSlotBytes = 2560;
+__host__ __device__ constexpr uint32_t swz(uint32_t off) { return off ^ (((off >> 7) & 3u) << 4); }
+constexpr uint32_t kRingLoS = kSmemBase + 2048;  // 512-aligned, like every slot; control data ends at 1536
+static_assert(kRingLoS % 512 == 0 && kRingHi % 512 == 0 && kSlotBytes % 512 == 0, "the swizzle follows address bits 7-8");
 constexpr int kLoSlotsS = (kLutAddr - kRingLoS) / kSlotBytes;
 constexpr uint32_t kPrefixAddr = kSmemEnd - 4224;  // int[kMaxBatch + 1] tiles before request b
 constexpr int kHiSlots = (kPrefixAddr - kRingHi) / kSlotBytes;
@@ -54,6 +66,7 @@ constexpr uint32_t kLevels = kSmemBase + 1280;    // fp16 [K|V][4][16]
 constexpr int kHdrNone = -1;
 
 constexpr int BKV_FLAG_DEBUG_NOLOAD = 0x100;  // timing experiment: reuse the first ring fill
+constexpr int BKV_FLAG_DEBUG_NOWAIT = 0x200;  // timing experiment (cp.async loader): consume tiles without waiting for them
 constexpr int BKV_FLAG_DEBUG_EQUAL_SHARES = 0x800;     // experiment: force equal shares
 constexpr int BKV_FLAG_DEBUG_ALIGNED_SHARES = 0x1000;  // experiment: force head-aligned shares
 
@@ -68,52 +81,20 @@ struct StreamParams {
   int aligned;   // 1: every CTA's share lies inside one head (heads get floor or ceil of C / heads CTAs)
 };
 
-// All bulk copies of one tile, issued by one elected lane of a converged warp in a single
-// predicated block (operands are warp-uniform).  Destination offsets follow the tile format.
-static_assert(kTilePayload == 2560 && kOffKHi == 528 && kOffKStat == 1040 && kOffVLo == 1296 && kOffVHi == 1824 &&
-                  kOffVStat == 2336 && kVStatSkew == 16,
-              "the offsets below are written out in the PTX text");
-__device__ __forceinline__ void issue_tile_page16(uint32_t dst, uint32_t bar, const char* kc, const char* ks,
-                                                  const char* vc, const char* vs) {
+// one box of the packed cache, seen as [page][64-byte row][64 bytes], into a ring slot
+// the V statistics of the four groups of one head for one 16-token tile: the region is seen as
+// [page][head*4+group][tile of the page][64 bytes]
+__device__ __forceinline__ void tensor_copy_4d(uint32_t dst, const CUtensorMap* map, int tile, int row, int page,
+                                               uint32_t bar) {
   asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "elect.sync _|p, 0xffffffff;\n"
-      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], 2560;\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%2], 512, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+528], [%2+512], 512, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1040], [%3], 256, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1296], [%4], 512, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1824], [%4+512], 512, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2336], [%5], 128, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2480], [%5+128], 128, [%1];\n"
-      "}\n" ::"r"(dst),
-      "r"(bar), "l"(kc), "l"(ks), "l"(vc), "l"(vs)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(map), "r"(0), "r"(tile), "r"(row), "r"(page), "r"(bar)
       : "memory");
 }
-// pages of more than 16 tokens: the V statistics of the four groups are `group_stride` bytes apart
-__device__ __forceinline__ void issue_tile_paged(uint32_t dst, uint32_t bar, const char* kc, const char* ks,
-                                                 const char* vc, const char* vs, int64_t group_stride) {
+__device__ __forceinline__ void tensor_copy_3d(uint32_t dst, const CUtensorMap* map, int row, int page, uint32_t bar) {
   asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .b64 v1, v2, v3;\n"
-      "add.s64 v1, %5, %6;\n"
-      "add.s64 v2, v1, %6;\n"
-      "add.s64 v3, v2, %6;\n"
-      "elect.sync _|p, 0xffffffff;\n"
-      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], 2560;\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%2], 512, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+528], [%2+512], 512, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1040], [%3], 256, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1296], [%4], 512, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+1824], [%4+512], 512, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2336], [%5], 64, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2400], [v1], 64, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2480], [v2], 64, [%1];\n"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0+2544], [v3], 64, [%1];\n"
-      "}\n" ::"r"(dst),
-      "r"(bar), "l"(kc), "l"(ks), "l"(vc), "l"(vs), "l"(group_stride)
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(0), "r"(row), "r"(page), "r"(bar)
       : "memory");
 }
 
@@ -129,11 +110,13 @@ struct Ring {
   }
 };
 
-// LOADER 0: bulk copies (cp.async.bulk) completing on one mbarrier per ring stage, issued by an
-// elected lane.  LOADER 1: every lane moves 16-byte pieces with cp.async, one commit group per
-// tile; the pieces land wherever the tile format wants them, at a fifth of the instructions.
+// LOADER 1: every lane moves 16-byte pieces with cp.async, one commit group per tile.
+// LOADER 3: an elected lane issues one tensor copy (cp.async.bulk.tensor) per part of a tile,
+// completing on one mbarrier per ring stage; the copies bypass the load/store pipe.
 template <int NW, int STAGES, bool STAT_BF16, int LOADER, int PAIR = 2>
-__global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamParams sp) {
+__global__ void __maxnreg__(max_regs_for(NW))
+    decode_stream_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap map16,
+                         const __grid_constant__ CUtensorMap map4, const __grid_constant__ CUtensorMap mapvs) {
   static_assert(STAGES <= 4, "cp_async_wait_pending handles up to three groups in flight");
   using R = Ring<NW, STAGES>;
   const DecodeParams& p = sp.d;
@@ -145,9 +128,9 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
   auto gptr = [&](uint32_t shared_addr) { return smem + (shared_addr - kSmemBase); };
   constexpr uint32_t kFull = 0xffffffffu;
   const int tid = threadIdx.x, lane = tid & 31;
-  // broadcast from lane 0 so that the compiler knows the warp index (and all the loop state
-  // derived from it) to be uniform across the warp
-  const int warp = __shfl_sync(kFull, tid >> 5, 0);
+  // a warp-wide reduction leaves its result in a uniform register, so the compiler knows the
+  // warp index (and all the loop state derived from it) to be uniform across the warp
+  const int warp = __reduce_max_sync(kFull, tid >> 5);
   const int gid = lane >> 2, tig = lane & 3;
   const int C = gridDim.x, cta = blockIdx.x;
   const int B = p.batch;
@@ -159,6 +142,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
   const int lo = max(p.token_lo, 0);
   const int page_lo = lo / BS;
   const bool noload = (p.flags & BKV_FLAG_DEBUG_NOLOAD) != 0;
+  const bool nowait = (p.flags & BKV_FLAG_DEBUG_NOWAIT) != 0;
 
   if (p.flags & BKV_FLAG_PDL_WAIT) pdl_wait();
   pdl_launch_dependents();  // the fix-up grid may be set up now; it waits for this grid to finish
@@ -243,25 +227,27 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
 
   // ---- per-lane roles (see the file comment) ----------------------------------------------
   const int ksel = tig >> 1, khalf = tig & 1;     // QK: this lane's k-slots carry half khalf of group 2*ksel+P
-  const int prow = (kRowSlot >> (4 * gid)) & 15;  // k-slot of the PV stage that QK row gid corresponds to
-  const int tq0 = static_cast<int>((kTokOfSlot >> (4 * prow)) & 15);  // row gid; row gid+8 is token tq0+4
-  const uint32_t kc_off = kOffKLo + code_row_off(tq0) + (2 * ksel) * 16 + khalf * 8;  // +16: pair 1, +256: row gid+8
-  const uint32_t ks_off = kOffKStat + tq0 * 16;                                        // +64: row gid+8
+  const int tq0 = gid;                            // QK rows gid / gid+8 carry tokens gid / gid+8
+  const uint32_t kc_off0 = swz(kSwKCode + tq0 * 64 + (2 * ksel) * 16) + khalf * 8;      // pair 0; +512: row gid+8
+  const uint32_t kc_off1 = swz(kSwKCode + tq0 * 64 + (2 * ksel + 1) * 16) + khalf * 8;  // pair 1
+  const uint32_t ks_off0 = swz(kSwKStat + tq0 * 16), ks_off1 = swz(kSwKStat + (tq0 + 8) * 16);
   const int vsel = gid >> 2, vu = gid & 3;        // PV: rows gid/gid+8 are dims 8*vu+2i(+1) of group 2*vsel+P
   const int hcol = gid >> 1, gsel = gid & 1;      // B column gid: query head hcol, group 2*gsel+P
-  int tk[2];                                      // tokens of k-slots 2tig, 2tig+1 (slots +8: tokens +4)
-  tk[0] = static_cast<int>((kTokOfSlot >> (4 * (2 * tig))) & 15);
-  tk[1] = static_cast<int>((kTokOfSlot >> (4 * (2 * tig + 1))) & 15);
-  const uint32_t vc_off0 = kOffVLo + code_row_off(tk[0]) + (2 * vsel) * 16 + vu * 4;  // +16: pair 1, +256: slots +8
-  const uint32_t vc_off1 = kOffVLo + code_row_off(tk[1]) + (2 * vsel) * 16 + vu * 4;
-  const uint32_t vs_off = kOffVStat + ((2 * gsel) * kTile + min(tk[0], tk[1])) * 4 + gsel * kVStatSkew;  // +64: pair 1, +16: slots +8
-  const bool pair_swapped = tk[0] > tk[1];  // odd tig: the pair sits in memory as (second, first)
-  const uint32_t sel_scale = pair_swapped ? 0x1054u : 0x5410u, sel_min = pair_swapped ? 0x3276u : 0x7632u;
+  // PV k-slots 2tig, 2tig+1 (+8) carry tokens tig, tig+4 (+8): four consecutive tokens per load
+  uint32_t vc_off[2][2];                          // [token tig / tig+4][pair]; +512: tokens +8
+#pragma unroll
+  for (int e = 0; e < 2; ++e)
+#pragma unroll
+    for (int P = 0; P < 2; ++P) vc_off[e][P] = swz(kSwVCode + (tig + 4 * e) * 64 + (2 * vsel + P) * 16) + vu * 4;
+  // V statistic word of (group 2*gsel+P, token tig+4e+8o): +64 for pair 1, +32 for o = 0 (the
+  // swizzle of this part flips the bit that o sets)
+  const uint32_t vs_off0 = swz(kSwVStat + (2 * gsel) * 64 + (tig + 8) * 4);
+  const uint32_t vs_off1 = swz(kSwVStat + (2 * gsel) * 64 + (tig + 4 + 8) * 4);
   const uint32_t klane0 = kLutAddr | (lane * 4), klane1 = klane0 + kLutBlock;
   const uint32_t vlane0 = kLutAddr | (lane * 4 + 128), vlane1 = vlane0 + kLutBlock;
   // probabilities travel from the QK layout (token by gid, head by tig) to the PV layout (token by tig, head by gid)
-  const int src_lane0 = ((kRowSlot >> (4 * (2 * tig))) & 15) * 4 + hcol;      // row holding k-slots 2tig, 2tig+8
-  const int src_lane1 = ((kRowSlot >> (4 * (2 * tig + 1))) & 15) * 4 + hcol;  // row holding k-slots 2tig+1, 2tig+9
+  const int src_lane0 = tig * 4 + hcol;        // row holding tokens tig, tig+8     (k-slots 2tig, 2tig+8)
+  const int src_lane1 = (tig + 4) * 4 + hcol;  // row holding tokens tig+4, tig+12  (k-slots 2tig+1, 2tig+9)
 
   // ---- ring state of this warp: tile number g of its lifetime lives in stage g % STAGES ----
   const uint32_t ring_base = R::base(warp);
@@ -315,30 +301,27 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
     const int total = wb - wa;
     const bool work = total > 0 && !dead;
 
-    // loader: one lane issues the bulk copies of a tile, so every operand is warp-uniform.
-    // Chunks: K codes of tokens 0-7 / 8-15 (512 B each), K statistics (256), V codes (512
-    // each), then V statistics: two 128 B chunks (groups 0-1, 2-3) for 16-token pages, else
-    // 64 B per group.
-    const uint32_t code_head = head * (BS * kWordsPerHead) * 4;
-    const char* const kc_src = reinterpret_cast<const char*>(p.cache) + geo.k_code_off * 4 + code_head;
-    const char* const ks_src = reinterpret_cast<const char*>(p.cache) + (geo.k_stat_off + head * (BS * 4)) * 4;
-    const char* const vc_src = reinterpret_cast<const char*>(p.cache) + geo.v_code_off * 4 + code_head;
-    const char* const vs_src = reinterpret_cast<const char*>(p.cache) + (geo.v_stat_off + head * (4 * BS)) * 4;
     // cp.async loader: lane l moves the l-th 16 bytes of each 512-byte half of the K and V
-    // codes; lanes 0-15 move the K statistics, lanes 16-31 the V statistics
+    // codes (tokens 0-7 / 8-15); lanes 0-15 move the K statistics, lanes 16-31 the V statistics
+    const uint32_t code_head = head * (BS * kWordsPerHead) * 4;
     const uint32_t ld_kcode = geo.k_code_off * 4 + code_head + lane * 16;
     const uint32_t ld_vcode = geo.v_code_off * 4 + code_head + lane * 16;
+    const uint32_t ld_code_dst = swz(lane * 16);  // the swizzle repeats every 512 bytes
     uint32_t ld_stat_src, ld_stat_dst, ld_stat_sub;
     if (lane < 16) {
       ld_stat_src = (geo.k_stat_off + head * (BS * 4)) * 4 + lane * 16;
-      ld_stat_dst = kOffKStat + lane * 16;
+      ld_stat_dst = swz(kSwKStat + lane * 16);
       ld_stat_sub = 256;
     } else {
       const int g = (lane - 16) >> 2, c = (lane - 16) & 3;  // 64 bytes per group and tile
       ld_stat_src = (geo.v_stat_off + head * (4 * BS) + g * BS) * 4 + c * 16;
-      ld_stat_dst = kOffVStat + g * 64 + c * 16 + (g >= 2 ? kVStatSkew : 0);
+      ld_stat_dst = swz(kSwVStat + g * 64 + c * 16);
       ld_stat_sub = 64;
     }
+    // tensor-copy loader: 64-byte rows of the four parts inside a page
+    const int row_kcode = (geo.k_code_off * 4 + code_head) >> 6;
+    const int row_kstat = ((geo.k_stat_off + head * (BS * 4)) * 4) >> 6;
+    const int row_vcode = (geo.v_code_off * 4 + code_head) >> 6;
 
     // request that holds tile x of the head (prefix[b] <= x < prefix[b+1])
     auto request_of = [&](int x) {
@@ -368,33 +351,36 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
         meta_cur = meta_nxt;
         meta_nxt = fetch_meta(j + 32);
       }
-      const uint32_t meta = __shfl_sync(kFull, meta_cur, j & 31);
+      // (a reduction rather than a shuffle: the result is uniform for the compiler, so the
+      // address arithmetic of the copies runs on the uniform datapath)
+      const uint32_t meta = __reduce_or_sync(kFull, lane == (j & 31) ? meta_cur : 0u);
       const bool bad = meta == 0xFFFFFFFFu;
       bad_mask = bad ? (bad_mask | (1u << stage)) : (bad_mask & ~(1u << stage));
       const uint32_t phys = bad ? 0u : (meta & ((1u << kMaxPagesLog2) - 1));
       const uint32_t sub = bad ? 0u : (meta >> kMaxPagesLog2);
       const uint32_t dst = ring_base + stage * kSlotBytes;
-      const int64_t pg = phys * page_bytes;
       if (LOADER == 1) {
         if (!bad) {
-          const char* const page = reinterpret_cast<const char*>(p.cache) + pg;
+          const char* const page = reinterpret_cast<const char*>(p.cache) + phys * page_bytes;
           const char* const kp = page + (ld_kcode + sub * 1024);
           const char* const vp = page + (ld_vcode + sub * 1024);
-          const uint32_t dl = dst + lane * 16;
-          cp_async16(dl + kOffKLo, kp);
-          cp_async16(dl + kOffKHi, kp + 512);
+          const uint32_t dl = dst + ld_code_dst;
+          cp_async16(dl + kSwKCode, kp);
+          cp_async16(dl + kSwKCode + 512, kp + 512);
           cp_async16(dst + ld_stat_dst, page + (ld_stat_src + sub * ld_stat_sub));
-          cp_async16(dl + kOffVLo, vp);
-          cp_async16(dl + kOffVHi, vp + 512);
+          cp_async16(dl + kSwVCode, vp);
+          cp_async16(dl + kSwVCode + 512, vp + 512);
         }
         cp_async_commit();
       } else {
         const uint32_t bar = bar_base + 8 * stage;
-        if (tiles_per_page == 1)
-          issue_tile_page16(dst, bar, kc_src + pg, ks_src + pg, vc_src + pg, vs_src + pg);
-        else
-          issue_tile_paged(dst, bar, kc_src + pg + sub * 1024, ks_src + pg + sub * 256, vc_src + pg + sub * 1024,
-                           vs_src + pg + sub * 64, static_cast<int64_t>(BS) * 4);
+        if (elect_one_sync()) {
+          mbar_arrive_expect_tx(bar, kSlotBytes);
+          tensor_copy_3d(dst + kSwKCode, &map16, row_kcode + sub * 16, phys, bar);
+          tensor_copy_3d(dst + kSwVCode, &map16, row_vcode + sub * 16, phys, bar);
+          tensor_copy_3d(dst + kSwKStat, &map4, row_kstat + sub * 4, phys, bar);
+          tensor_copy_4d(dst + kSwVStat, &mapvs, sub, head * 4, phys, bar);
+        }
       }
       ++n_issued;
     };
@@ -449,11 +435,11 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
       float sacc[NT][2][4];
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint32_t ka = sb[t] + kc_off;
 #pragma unroll
         for (int P = 0; P < 2; ++P) {
-          const uint2 k0 = P ? ring_load64<16>(ka) : ring_load64<0>(ka);
-          const uint2 k1 = P ? ring_load64<16 + 256>(ka) : ring_load64<256>(ka);
+          const uint32_t ka = sb[t] + (P ? kc_off1 : kc_off0);
+          const uint2 k0 = ring_load64<0>(ka);    // token gid
+          const uint2 k1 = ring_load64<512>(ka);  // token gid+8
           const uint32_t w0[2] = {k0.x, k0.y}, w1[2] = {k1.x, k1.y};
           const uint32_t kl = P ? klane1 : klane0;
           uint32_t av[4][4];
@@ -475,15 +461,13 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
       uint32_t vidx[NT][2][2][2];  // [tile][pair][k-slots 2tig.. / 2tig+8..][row gid / row gid+8]
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint32_t va = sb[t] + vc_off0, vb = sb[t] + vc_off1;
 #pragma unroll
         for (int P = 0; P < 2; ++P)
 #pragma unroll
           for (int o = 0; o < 2; ++o) {
-            const uint32_t xa = P ? (o ? ring_load32<16 + 256>(va) : ring_load32<16>(va))
-                                  : (o ? ring_load32<256>(va) : ring_load32<0>(va));
-            const uint32_t xb = P ? (o ? ring_load32<16 + 256>(vb) : ring_load32<16>(vb))
-                                  : (o ? ring_load32<256>(vb) : ring_load32<0>(vb));
+            const uint32_t va = sb[t] + vc_off[0][P], vb = sb[t] + vc_off[1][P];
+            const uint32_t xa = o ? ring_load32<512>(va) : ring_load32<0>(va);  // token tig (+8)
+            const uint32_t xb = o ? ring_load32<512>(vb) : ring_load32<0>(vb);  // token tig+4 (+8)
             vidx[t][P][o][0] = (xa & 0x0F0F0F0Fu) | ((xb << 4) & 0xF0F0F0F0u);
             vidx[t][P][o][1] = ((xa >> 4) & 0x0F0F0F0Fu) | (xb & 0xF0F0F0F0u);
           }
@@ -492,10 +476,9 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
       float sc[NT][2];
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint32_t sa = sb[t] + ks_off;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          const uint4 st = r ? ring_load128i<64>(sa) : ring_load128i<0>(sa);  // groups 0..3
+          const uint4 st = ring_load128i<0>(sb[t] + (r ? ks_off1 : ks_off0));  // groups 0..3
           const float2 g0 = stat_word_to_f32<STAT_BF16>(st.x), g1 = stat_word_to_f32<STAT_BF16>(st.y);
           const float2 g2 = stat_word_to_f32<STAT_BF16>(st.z), g3 = stat_word_to_f32<STAT_BF16>(st.w);
           float u = g0.x * sacc[t][0][2 * r];       // column 2tig: group P, column 2tig+1: group P+2
@@ -508,7 +491,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
           v = fmaf(g3.y, qs[3], v);
           float x = u + v;
           if (PARTIAL) {  // behind the end of the sequence (statistics may be NaN)
-            if (tq0 + 4 * r >= nv[t]) x = -CUDART_INF_F;
+            if (tq0 + 8 * r >= nv[t]) x = -CUDART_INF_F;
           }
           sc[t][r] = x;
         }
@@ -540,7 +523,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
       for (int t = 0; t < NT; ++t) {
         const float e0 = fast_exp2(sc[t][0] - m_used), e1 = fast_exp2(sc[t][1] - m_used);
         l_run += e0 + e1;
-        const uint32_t mine = pack_half2(e0, e1);  // head tig: (token tq0, token tq0+4)
+        const uint32_t mine = pack_half2(e0, e1);  // head tig: (token gid, token gid+8)
         const uint32_t fromA = __shfl_sync(kFull, mine, src_lane0);  // tokens of k-slots 2tig, 2tig+8
         const uint32_t fromB = __shfl_sync(kFull, mine, src_lane1);  // tokens of k-slots 2tig+1, 2tig+9
         ph2[t][0] = __byte_perm(fromA, fromB, 0x5410);
@@ -549,26 +532,28 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
       // ------------------------------ per tile: W = p*scale_v, p*min_v, then O += Lv^T * W ----
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint32_t sa = sb[t] + vs_off;
+        const uint32_t sa0 = sb[t] + vs_off0, sa1 = sb[t] + vs_off1;
 #pragma unroll
         for (int P = 0; P < 2; ++P) {
           uint32_t wb2[2], mb2[2];
 #pragma unroll
           for (int o = 0; o < 2; ++o) {
-            const uint2 vs = P ? (o ? ring_load64<64 + 16>(sa) : ring_load64<64>(sa))
-                               : (o ? ring_load64<16>(sa) : ring_load64<0>(sa));
+            // statistic words of tokens tig+8o and tig+4+8o
+            const uint32_t fst = P ? (o ? ring_load32<64>(sa0) : ring_load32<64 + 32>(sa0))
+                                   : (o ? ring_load32<0>(sa0) : ring_load32<32>(sa0));
+            const uint32_t snd = P ? (o ? ring_load32<64>(sa1) : ring_load32<64 + 32>(sa1))
+                                   : (o ? ring_load32<0>(sa1) : ring_load32<32>(sa1));
             uint32_t sc2, mn2;
             if (STAT_BF16) {
-              const uint32_t fst = pair_swapped ? vs.y : vs.x, snd = pair_swapped ? vs.x : vs.y;
               sc2 = pack_half2(__uint_as_float(fst << 16), __uint_as_float(snd << 16));
               mn2 = pack_half2(__uint_as_float(fst & 0xFFFF0000u), __uint_as_float(snd & 0xFFFF0000u));
             } else {
-              sc2 = __byte_perm(vs.x, vs.y, sel_scale);
-              mn2 = __byte_perm(vs.x, vs.y, sel_min);
+              sc2 = __byte_perm(fst, snd, 0x5410);
+              mn2 = __byte_perm(fst, snd, 0x7632);
             }
             uint32_t wv = hmul2_u32(ph2[t][o], sc2), mv = hmul2_u32(ph2[t][o], mn2);
             if (PARTIAL) {  // 0 * NaN would poison the accumulators
-              const uint32_t keep = (tk[0] + 4 * o < nv[t] ? 0x0000FFFFu : 0u) | (tk[1] + 4 * o < nv[t] ? 0xFFFF0000u : 0u);
+              const uint32_t keep = (tig + 8 * o < nv[t] ? 0x0000FFFFu : 0u) | (tig + 4 + 8 * o < nv[t] ? 0xFFFF0000u : 0u);
               wv &= keep;
               mv &= keep;
             }
@@ -647,7 +632,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
         const uint32_t phaseB = s + 1 == STAGES ? phase ^ 1u : phase;
         // (the timing experiment stops issuing after the first fill and so stops waiting too)
         if (LOADER == 1) {
-          if (n_done < n_issued) {
+          if (n_done < n_issued && !nowait) {
             cp_async_wait_pending(n_issued - n_done - cnt);  // this thread's pieces of the tile(s) ...
             __syncwarp();                                     // ... and every other lane's
           }
@@ -670,7 +655,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
         // the stages are free again: refill them with the tiles STAGES ahead
         if (!noload) {
           __syncwarp();
-          if (LOADER == 0) fence_proxy_async();
+          if (LOADER != 1) fence_proxy_async();  // reads of the generic proxy before writes of the async proxy
           if (run_done + STAGES < total) issue(run_done + STAGES, s);
           if (cnt == 2 && run_done + 1 + STAGES < total) issue(run_done + 1 + STAGES, sB);
         }
@@ -737,7 +722,7 @@ __global__ void __maxnreg__(max_regs_for(NW)) decode_stream_kernel(const StreamP
   }
 
   if (LOADER == 1) cp_async_wait_group<0>();
-  if (LOADER == 0 && dead) {  // let the copies still in flight land before the shared memory is given back
+  if (LOADER != 1 && dead) {  // let the copies still in flight land before the shared memory is given back
     for (int g = n_done; g < n_issued; ++g) {
       const int st = g % STAGES;
       WaitBudget budget;
@@ -908,6 +893,85 @@ __global__ void __launch_bounds__(1024) stream_prefix_kernel(const DecodeParams 
 constexpr int64_t kPartialBytes = 4 * kHeadDim * 4 + 16 + 16 + 4;  // o, m, l of four heads and the header
 constexpr int64_t kPlannedPrefixBytes = (kMaxBatchPlanned + 64) * 4;  // a multiple of 256
 
+// ---- tensor maps of the packed cache ------------------------------------------------------------
+// The cache is described as uint8 [page][64-byte row][64]; a box is `rows` rows of one page,
+// stored with the 64-byte swizzle.  Maps are cached per (cache, geometry, box).
+struct CacheMaps {
+  CUtensorMap map16, map4, mapvs;
+};
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+bool make_cache_map(CUtensorMap* out, const DecodeParams& p, int rows) {
+  const EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  const PageGeom geo = make_geom(p.block_size, p.heads_kv);
+  const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(geo.block_i32) * 4 / 64, static_cast<cuuint64_t>(p.num_pages)};
+  const cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(p.page_stride) * 4};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint32_t*>(p.cache), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_vstat_map(CUtensorMap* out, const DecodeParams& p) {
+  const EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  const PageGeom geo = make_geom(p.block_size, p.heads_kv);
+  const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(p.block_size / 16), static_cast<cuuint64_t>(p.heads_kv) * 4,
+                              static_cast<cuuint64_t>(p.num_pages)};
+  const cuuint64_t strides[3] = {64, static_cast<cuuint64_t>(p.block_size) * 4, static_cast<cuuint64_t>(p.page_stride) * 4};
+  const cuuint32_t box[4] = {64, 1, 4, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  void* base = const_cast<uint32_t*>(p.cache) + geo.v_stat_off;
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// false: the driver offers no tensor maps for this cache (then the cp.async loader is used)
+bool cache_maps_for(const DecodeParams& p, CacheMaps* out) {
+  struct Entry {
+    const void* cache;
+    int64_t pages, stride;
+    int block, heads, dev;
+    CacheMaps maps;
+    bool ok;
+  };
+  static std::mutex mu;
+  static Entry slots[8] = {};
+  static int next = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  for (const Entry& e : slots)
+    if (e.cache == p.cache && e.pages == p.num_pages && e.stride == p.page_stride && e.block == p.block_size &&
+        e.heads == p.heads_kv && e.dev == dev && e.cache != nullptr) {
+      *out = e.maps;
+      return e.ok;
+    }
+  Entry& e = slots[next];
+  next = (next + 1) % 8;
+  e = Entry{p.cache, p.num_pages, p.page_stride, p.block_size, p.heads_kv, dev, {}, false};
+  e.ok = (p.page_stride * 4) % 64 == 0 && make_cache_map(&e.maps.map16, p, 16) && make_cache_map(&e.maps.map4, p, 4) &&
+         make_vstat_map(&e.maps.mapvs, p);
+  *out = e.maps;
+  return e.ok;
+}
+
 template <int NW, int STAGES, int LOADER, int PAIR = 2>
 int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_seq_len, int sm_count,
                    cudaStream_t stream) {
@@ -950,6 +1014,8 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
     if (rcp != BKV_OK) return rcp;
   }
 
+  CacheMaps maps = {};
+  if (LOADER == 3 && !cache_maps_for(p, &maps)) return BKV_ERR_UNSUPPORTED;
   auto kern = p.stat_bf16 ? decode_stream_kernel<NW, STAGES, true, LOADER, PAIR>
                           : decode_stream_kernel<NW, STAGES, false, LOADER, PAIR>;
   static bool configured[2][64] = {};
@@ -966,7 +1032,7 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
     }
     configured[p.stat_bf16 ? 1 : 0][dev] = true;
   }
-  kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp);
+  kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp, maps.map16, maps.map4, maps.mapvs);
   int rc = check_launch("bkv_decode_stream_sm100(decode)");
   if (rc != BKV_OK) return rc;
   // programmatic dependent launch: the fix-up grid is set up while the decode grid drains
@@ -1017,15 +1083,12 @@ int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, int 
   const int sms = device_sm_count();
   if (sms <= 0) return BKV_ERR_CUDA;
   switch (config) {
-    case 1: return launch_variant<8, 4, 0>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 2: return launch_variant<12, 3, 0>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 3: return launch_variant<16, 2, 0>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 1: return launch_variant<8, 4, 3>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 2: return launch_variant<12, 3, 3>(p, ws, ws_bytes, max_seq_len, sms, stream);
+    case 3: return launch_variant<16, 2, 3>(p, ws, ws_bytes, max_seq_len, sms, stream);
     case 5: return launch_variant<12, 3, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
     case 6: return launch_variant<8, 4, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
     case 7: return launch_variant<16, 2, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 8: return launch_variant<9, 4, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 9: return launch_variant<12, 3, 1, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 10: return launch_variant<16, 2, 1, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
     default: return launch_variant<12, 3, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
   }
 }

@@ -102,7 +102,7 @@ def test_long_context_many_splits(variant):
         _check(q, cache, bt, lens, 2, 16, lk, lv, "bf16", splits=splits, variant=variant)
 
 
-@pytest.mark.parametrize("variant", [40, 41, 43, 45, 46, 47])
+@pytest.mark.parametrize("variant", [40, 41, 42, 43, 45, 46, 47])
 @pytest.mark.parametrize("bs,heads_kv,gqa,kind", [(16, 2, 4, "bf16"), (64, 4, 8, "f16"), (32, 3, 2, "bf16")])
 def test_persistent_schedule_cut_requests(bs, heads_kv, gqa, kind, variant):
     """Many ragged requests under the persistent schedule: workers cut requests at arbitrary
