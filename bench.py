@@ -64,6 +64,8 @@ def parse_args():
     ap.add_argument("--dense-baseline", action="store_true",
                     help="also time bf16-KV decode attention on the same shapes: this library's plain kernel and, "
                          "when importable, flash_attn's flash_attn_with_kvcache (library code, reported as such)")
+    ap.add_argument("--e2e-eager", action="store_true",
+                    help="issue the end-to-end step's calls directly instead of replaying a captured CUDA graph")
     ap.add_argument("--sweep", action="store_true",
                     help="context sweep 1K..128K at 4M KV tokens on one GPU, with the bf16-KV baselines")
     return ap.parse_args()
@@ -332,35 +334,70 @@ def measure(args, world, rank, local_rank, dev):
     value = world * packed_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- end-to-end serving step with host inputs --------------------------------------
+    # The caller's step: fill one pinned staging buffer (q | new K row | new V row | seq_lens |
+    # slots), one host->device copy, encode-on-write, decode, one device->host copy of the
+    # output, wait.  The device part is captured once into a CUDA graph through the public API
+    # (the launcher neither allocates nor synchronises) and replayed per step, the way a serving
+    # engine drives it; --e2e-eager issues the same calls directly.
     e2e_steps = min(args.steps, 500)
-    h_q = torch.randn((B, HEADS_Q, HEAD_DIM)).to(torch.bfloat16).pin_memory()
-    h_k = torch.randn((B, HEADS_KV, HEAD_DIM)).to(torch.bfloat16).pin_memory()
-    h_v = torch.randn((B, HEADS_KV, HEAD_DIM)).to(torch.bfloat16).pin_memory()
+    nq, nkv = B * HEADS_Q * HEAD_DIM, B * HEADS_KV * HEAD_DIM
+    stage_bytes = (nq + 2 * nkv) * 2 + 2 * B * 4
+    h_in = torch.empty((stage_bytes,), dtype=torch.uint8).pin_memory()
+    d_in = torch.empty((stage_bytes,), dtype=torch.uint8, device=dev)
+
+    def views(buf):
+        o1, o2, o3, o4 = nq * 2, (nq + nkv) * 2, (nq + 2 * nkv) * 2, (nq + 2 * nkv) * 2 + B * 4
+        return (buf[:o1].view(torch.bfloat16).view(B, HEADS_Q, HEAD_DIM),
+                buf[o1:o2].view(torch.bfloat16).view(B, HEADS_KV, HEAD_DIM),
+                buf[o2:o3].view(torch.bfloat16).view(B, HEADS_KV, HEAD_DIM),
+                buf[o3:o4].view(torch.int32), buf[o4:].view(torch.int32))
+
+    h_q, h_k, h_v, h_lens, h_slots = views(h_in)
+    d_q, d_k, d_v, d_lens, d_slots = views(d_in)
+    h_q.copy_(torch.randn((B, HEADS_Q, HEAD_DIM)).to(torch.bfloat16))
+    h_k.copy_(torch.randn((B, HEADS_KV, HEAD_DIM)).to(torch.bfloat16))
+    h_v.copy_(torch.randn((B, HEADS_KV, HEAD_DIM)).to(torch.bfloat16))
     h_out = torch.empty((B, HEADS_Q, HEAD_DIM), dtype=torch.bfloat16).pin_memory()
     bt_cpu = block_table.cpu()
-    h_lens = torch.empty((B,), dtype=torch.int32).pin_memory()
-    h_slots = torch.empty((B,), dtype=torch.int32).pin_memory()
-    d_q, d_k, d_v = torch.empty_like(q), torch.empty((B, HEADS_KV, HEAD_DIM), dtype=torch.bfloat16, device=dev), None
-    d_v = torch.empty_like(d_k)
-    d_lens = torch.empty((B,), dtype=torch.int32, device=dev)
-    d_slots = torch.empty((B,), dtype=torch.int32, device=dev)
     spare = BS  # tokens of head-room in the last page
 
-    def e2e_step(i: int):
-        pos = ctx + (i % spare)  # position of the appended token
-        h_lens.fill_(pos + 1)
-        h_slots.copy_(bt_cpu[:, pos // BS] * BS + pos % BS)
-        d_q.copy_(h_q, non_blocking=True)
-        d_k.copy_(h_k, non_blocking=True)
-        d_v.copy_(h_v, non_blocking=True)
-        d_lens.copy_(h_lens, non_blocking=True)
-        d_slots.copy_(h_slots, non_blocking=True)
+    def device_part():
+        d_in.copy_(h_in, non_blocking=True)
         write_tokens_to_paged_cache(cache, layout, block_table, d_slots, d_k, d_v, q_points_k=lk, q_points_v=lv,
                                     thresholds_k=tk, thresholds_v=tv, require_fast=True, stat_dtype=stat_dtype)
         rt.run_nonuniform_decode(spec=spec, q=d_q, cache=cache, layout=layout, block_table=block_table,
                                  seq_lens=d_lens, k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
                                  workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
         h_out.copy_(out, non_blocking=True)
+
+    def host_inputs(i: int):
+        pos = ctx + (i % spare)  # position of the appended token
+        h_lens.fill_(pos + 1)
+        h_slots.copy_(bt_cpu[:, pos // BS] * BS + pos % BS)
+
+    graph, e2e_mode = None, "eager"
+    if not args.e2e_eager:
+        try:
+            host_inputs(0)
+            device_part()  # every lazily created resource exists before the capture
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                device_part()
+            torch.cuda.current_stream().wait_stream(side)
+            graph, e2e_mode = g, "cuda_graph"
+        except Exception as exc:  # capture not possible here: time the eager calls and say so
+            graph, e2e_mode = None, f"eager (graph capture failed: {exc!r})"
+            torch.cuda.synchronize()
+
+    def e2e_step(i: int):
+        host_inputs(i)
+        if graph is not None:
+            graph.replay()
+        else:
+            device_part()
         torch.cuda.current_stream().synchronize()  # the caller needs the result of this step
 
     for i in range(3):
@@ -374,7 +411,7 @@ def measure(args, world, rank, local_rank, dev):
     sync_all()
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3
     e2e_ms = max_over_ranks(max(ev0.elapsed_time(ev1), 0.0)) / e2e_steps
-    h2d = (h_q.numel() + h_k.numel() + h_v.numel()) * 2 + (h_lens.numel() + h_slots.numel()) * 4
+    h2d = stage_bytes
     d2h = h_out.numel() * 2
     e2e_value = world * packed_bytes / (e2e_ms * 1e-3) / 1e9
 
@@ -413,7 +450,7 @@ def measure(args, world, rank, local_rank, dev):
                 "traffic": ncu_traffic_bytes(workload_key),
                 "note": "duration is the whole step (decode kernel + combine kernel when split)",
             },
-            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "mode": e2e_mode, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             **({"experiment": f"block table folded onto {args.experiment_hot_pages} pages (L2-resident): not a "
                               "bandwidth measurement"} if args.experiment_hot_pages > 0 else {}),
