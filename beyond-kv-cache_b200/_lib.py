@@ -38,6 +38,7 @@ SIGNATURES = {
     "bkv_decode_stream_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _I, _P,
                                 _P, _L, _I, _I, _I, _F, _I, _I, _P],
     "bkv_decode_stream_workspace_bytes": [],
+    "bkv_selftest_division_sm100": [_c.c_uint64, _L, _I, _P, _P],
     "bkv_decode_device_status": [_P],
     "bkv_combine_sm100": [_P, _P, _P, _I, _L, _P, _I, _P, _P],
     "bkv_decode_range_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _P,

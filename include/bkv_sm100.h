@@ -111,6 +111,18 @@ int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const v
                      bkv_stream_t stream);
 
 /*
+ * Test hook (no counterpart in the reference): the encoder divides by the group scale with
+ * a reciprocal shared by the 8 scalars of a lane and an exact-remainder correction; this
+ * entry point runs that division next to the IEEE division (__fdiv_rn) on `count`
+ * pseudo-random operand pairs and ADDS the number of bitwise mismatches to *mismatches
+ * (device memory, 64-bit, zeroed by the caller).  mode 0: the quantiser's domain
+ * (divisor in [2^-20, 2^6), dividend in [0, divisor]); mode 1: any finite positive pair.
+ * The expected count is 0 in both modes.
+ */
+int bkv_selftest_division_sm100(uint64_t seed, int64_t count, int mode, unsigned long long* mismatches,
+                                bkv_stream_t stream);
+
+/*
  * Persistent form of bkv_decode_sm100: same inputs and results, different schedule.
  *
  * Replaces the same reference launcher as bkv_decode_sm100

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import oracle
-from beyond_kv_cache_b200 import synth
+from beyond_kv_cache_b200 import _lib, synth
 from beyond_kv_cache_b200.quant.beyond_cute import (
     CODE_LAYOUT_HEAD_WORD_TOKEN,
     CODE_LAYOUT_HND_TOKEN_WORD,
@@ -162,3 +162,15 @@ def test_empty_and_rejected_inputs():
                                     torch.zeros((1,), dtype=torch.int32, device=DEV),
                                     torch.zeros((1, 2, 96), dtype=torch.float16, device=DEV),
                                     torch.zeros((1, 2, 96), dtype=torch.float16, device=DEV), require_fast=True)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_shared_divisor_division_is_the_ieee_division(mode):
+    """The encoder's division by a shared divisor (reciprocal + exact-remainder correction)
+    against __fdiv_rn on 2^28 pseudo-random operand pairs: zero bitwise mismatches, both in
+    the quantiser's operand domain and over all finite positive pairs."""
+    bad = torch.zeros((1,), dtype=torch.int64, device="cuda")
+    for seed in (1, 2):
+        _lib.call("bkv_selftest_division_sm100", seed, 1 << 27, mode, bad.data_ptr(), _lib.current_stream(bad.device))
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0
