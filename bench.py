@@ -66,6 +66,12 @@ def parse_args():
                          "when importable, flash_attn's flash_attn_with_kvcache (library code, reported as such)")
     ap.add_argument("--e2e-eager", action="store_true",
                     help="issue the end-to-end step's calls directly instead of replaying a captured CUDA graph")
+    ap.add_argument("--serve", action="store_true",
+                    help="encode-on-write plus decode at serving batch: 256 sequences prefill 1024 K/V tokens into "
+                         "the packed cache, then 128 decode steps append one token each and run attention")
+    ap.add_argument("--kv-split", action="store_true",
+                    help="one 128K-token sequence whose KV range is split over the ranks (torchrun): per-rank "
+                         "range decode, NCCL all-gather of the partials, log-sum-exp merge on every rank")
     ap.add_argument("--sweep", action="store_true",
                     help="context sweep 1K..128K at 4M KV tokens on one GPU, with the bf16-KV baselines")
     return ap.parse_args()
@@ -237,6 +243,22 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.kv_split:
+        line = measure_kv_split(args, world, rank, local_rank, dev)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+    if args.serve:
+        line = measure_serve(args, world, rank, local_rank, dev)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if args.sweep:
         # context sweep at a constant 4M KV tokens (batch = 4M / context), one JSON line per point
         points = [(4096, 1024), (1024, 4096), (256, 16384), (128, 32768), (64, 65536), (32, 131072)]
@@ -254,6 +276,163 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def measure_kv_split(args, world, rank, local_rank, dev, ctx: int = 131072):
+    """One sequence of `ctx` tokens; rank r holds and attends only its page-aligned share of the
+    KV range (strong scaling); the un-normalised partials (32 heads x 130 floats per rank) are
+    all-gathered over NCCL and merged on every rank."""
+    import torch
+    import torch.distributed as dist
+
+    from beyond_kv_cache_b200 import parallel, synth
+    from beyond_kv_cache_b200.quant.beyond_cute import PagedLayout, write_tokens_to_paged_cache
+
+    BS = args.page
+    stat_dtype = torch.float16 if args.stat == "fp16" else torch.bfloat16
+    layout = PagedLayout.build_hnd(BS, HEADS_KV, HEAD_DIM, 4, 32, 32)
+    lo, hi = parallel.kv_range_for_rank(ctx, BS, world, rank)
+    pages_total = (ctx + BS - 1) // BS
+    # the block table names every page of the sequence; only this rank's range is filled
+    block_table, num_pages = synth.random_block_table(1, pages_total, seed=3, device=dev)
+    cache = torch.zeros((num_pages, layout.block_i32), dtype=torch.int32, device=dev)
+    lk, tk = (t.to(dev) for t in synth.make_tables(HEADS_KV, seed=0, which="k"))
+    lv, tv = (t.to(dev) for t in synth.make_tables(HEADS_KV, seed=0, which="v"))
+    if hi > lo:
+        k, v = synth.make_kv(hi - lo, HEADS_KV, seed=11 + rank, device=dev)
+        write_tokens_to_paged_cache(cache, layout, block_table, synth.slots_for(block_table, BS, lo, hi - lo), k, v,
+                                    q_points_k=lk, q_points_v=lv, thresholds_k=tk, thresholds_v=tv,
+                                    require_fast=True, stat_dtype=stat_dtype)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)  # the same query on every rank
+    q = torch.randn((1, HEADS_Q, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
+    seq_lens = torch.full((1,), ctx, dtype=torch.int32, device=dev)
+    out = torch.empty((1, HEADS_Q, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+    scale = synth.softmax_scale()
+
+    def step():
+        parallel.decode_kv_range_split(q, cache, layout, block_table, seq_lens, lk, lv, out, token_lo=lo, token_hi=hi,
+                                       softmax_scale=scale, stat_dtype=stat_dtype)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps = min(args.steps, 500)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank != 0:
+        return None
+    nbytes = ctx * HEADS_KV * BYTES_PER_TOKEN_HEAD
+    return {
+        "metric": "kv_range_split_decode_attention",
+        "value": nbytes / (ms * 1e-3) / 1e9,
+        "unit": "GB/s",
+        "n_gpus": world,
+        "us_per_layer": ms * 1e3,
+        "scaling": "strong",
+        "config": {"workload": f"one sequence x ctx {ctx}, {HEADS_Q} q / {HEADS_KV} kv heads, {BS}-token pages, "
+                               f"KV range split over {world} GPU(s), NCCL all-gather of (o, m, l) + merge"},
+        "data": "synthetic",
+    }
+
+
+def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: int = 1024, gen_steps: int = 128):
+    """Encode-on-write + decode at serving batch (one layer): prefill `seqs` x `prompt` bf16
+    K/V tokens through the encode kernel, then `gen_steps` decode steps, each appending one
+    token per sequence (encode) and attending the whole packed context (decode)."""
+    import torch
+    import torch.distributed as dist
+
+    from beyond_kv_cache_b200 import synth
+    from beyond_kv_cache_b200.quant.beyond_cute import PagedLayout, write_tokens_to_paged_cache
+    from beyond_kv_cache_b200.quant.fa4_cute import beyond_mixed_decode_runtime as rt
+
+    BS = args.page
+    stat_dtype = torch.float16 if args.stat == "fp16" else torch.bfloat16
+    layout = PagedLayout.build_hnd(BS, HEADS_KV, HEAD_DIM, 4, 32, 32)
+    pages_per_seq = (prompt + gen_steps + BS - 1) // BS
+    block_table, num_pages = synth.random_block_table(seqs, pages_per_seq, seed=rank, device=dev)
+    cache = torch.zeros((num_pages, layout.block_i32), dtype=torch.int32, device=dev)
+    lk, tk = (t.to(dev) for t in synth.make_tables(HEADS_KV, seed=0, which="k"))
+    lv, tv = (t.to(dev) for t in synth.make_tables(HEADS_KV, seed=0, which="v"))
+    rk, rv = rt.prepare_runtime_qpoints(lk, lv, heads_kv=HEADS_KV)
+    k, v = synth.make_kv(seqs * prompt, HEADS_KV, seed=7 + rank, device=dev)
+    slots = synth.slots_for(block_table, BS, 0, prompt)
+
+    def encode(kk, vv, ss):
+        write_tokens_to_paged_cache(cache, layout, block_table, ss, kk, vv, q_points_k=lk, q_points_v=lv,
+                                    thresholds_k=tk, thresholds_v=tv, require_fast=True, stat_dtype=stat_dtype)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    prefill_ms = timed(lambda: encode(k, v, slots), 20)
+    prefill_bytes = seqs * prompt * HEADS_KV * (512 + 160)  # bf16 K and V rows in, packed row out
+
+    q = torch.randn((seqs, HEADS_Q, HEAD_DIM), device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    k1, v1 = synth.make_kv(seqs, HEADS_KV, seed=99 + rank, device=dev)
+    spec = rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=block_table, heads_q=HEADS_Q,
+                                max_seq_len=pages_per_seq * BS, num_splits=args.splits)
+    ws = rt.allocate_runtime_workspace(spec, device=dev)
+    lens = [torch.full((seqs,), prompt + i + 1, dtype=torch.int32, device=dev) for i in range(gen_steps)]
+    step_slots = [synth.slots_for(block_table, BS, prompt + i, 1) for i in range(gen_steps)]
+    scale = synth.softmax_scale()
+
+    def generate():
+        for i in range(gen_steps):
+            encode(k1, v1, step_slots[i])
+            rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=block_table,
+                                     seq_lens=lens[i], k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
+                                     workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
+
+    gen_ms = timed(generate, 5)
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peak()
+    attended = sum((prompt + i + 1) for i in range(gen_steps)) * seqs * HEADS_KV * BYTES_PER_TOKEN_HEAD
+    return {
+        "metric": "serve_encode_decode_one_layer",
+        "value": world * seqs * gen_steps / (gen_ms * 1e-3),
+        "unit": "decode tokens/s (one layer)",
+        "n_gpus": world,
+        "config": {"workload": f"{seqs} sequences/GPU x {prompt}-token prefill + {gen_steps} decode steps, "
+                               f"{HEADS_Q} q / {HEADS_KV} kv heads, {BS}-token pages"},
+        "prefill_encode": {"ms": prefill_ms, "tokens": seqs * prompt,
+                           "GBps": prefill_bytes / (prefill_ms * 1e-3) / 1e9,
+                           "frac_of_peak": prefill_bytes / (prefill_ms * 1e-3) / 1e9 / peak,
+                           "bytes_per_token_head": 672, "peak_source": peak_kind},
+        "decode_steps": {"ms_per_step": gen_ms / gen_steps, "steps": gen_steps,
+                         "attended_GBps": attended / (gen_ms * 1e-3) / 1e9},
+        "data": "synthetic",
+    }
 
 
 def measure(args, world, rank, local_rank, dev):

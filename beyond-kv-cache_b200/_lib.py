@@ -43,6 +43,9 @@ SIGNATURES = {
     "bkv_combine_sm100": [_P, _P, _P, _I, _L, _P, _I, _P, _P],
     "bkv_decode_range_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _P,
                                _P, _I, _I, _I, _I, _F, _I, _P],
+    "bkv_combine_packed_sm100": [_P, _I, _L, _P, _I, _P, _P],
+    "bkv_decode_range_stream_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _P,
+                                      _P, _P, _L, _I, _I, _I, _I, _F, _I, _I, _P],
     "bkv_readback_sm100": [_P, _L, _L, _I, _I, _I, _P, _L, _L, _P, _P, _I, _I, _P, _P, _I, _I, _I,
                            _P, _P, _I, _P],
     "bkv_decode_dense_sm100": [_P, _L, _I, _P, _P, _I, _L, _I, _I, _P, _L, _P, _P, _I, _P, _P, _P,

@@ -179,6 +179,46 @@ extern "C" int bkv_combine_sm100(const float* o_partial, const float* m_partial,
                         static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int bkv_combine_packed_sm100(const float* records, int num_splits, int64_t rows, void* out,
+                                        int out_dtype, float* out_f32, bkv_stream_t stream) {
+  using namespace bkv;
+  if (num_splits < 1 || rows < 0) return BKV_ERR_ARG;
+  if (rows == 0) return BKV_OK;
+  if (!records || !out) return BKV_ERR_ARG;
+  if (out_dtype != BKV_F16 && out_dtype != BKV_BF16 && out_dtype != BKV_F32) return BKV_ERR_ARG;
+  return launch_combine_packed(records, num_splits, rows, out, out_dtype, out_f32,
+                               static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bkv_decode_range_stream_sm100(const void* q, int64_t q_batch_stride, int q_dtype,
+                                             const void* cache, int64_t num_pages,
+                                             int64_t page_stride_i32, int block_size, int heads_kv,
+                                             int stat_dtype, const int32_t* block_table,
+                                             int64_t block_table_stride, const int32_t* seq_lens,
+                                             const void* lvl_k, const void* lvl_v, int table_dtype,
+                                             float* o_partial, float* m_partial, float* l_partial,
+                                             void* workspace, int64_t workspace_bytes, int batch,
+                                             int heads_q, int token_lo, int token_hi,
+                                             float softmax_scale, int flags, int variant,
+                                             bkv_stream_t stream) {
+  using namespace bkv;
+  DecodeParams p;
+  const int rc = fill_decode_params(p, q, q_batch_stride, q_dtype, cache, num_pages,
+                                    page_stride_i32, block_size, heads_kv, stat_dtype, block_table,
+                                    block_table_stride, seq_lens, lvl_k, lvl_v, table_dtype, batch,
+                                    heads_q, softmax_scale, flags);
+  if (rc != BKV_OK) return rc;
+  if (batch == 0) return BKV_OK;
+  if (!o_partial || !m_partial || !l_partial || !workspace) return BKV_ERR_ARG;
+  if (token_lo < 0 || token_hi < token_lo) return BKV_ERR_ARG;
+  if (token_lo % block_size) return BKV_ERR_ARG;  // ranges start on a page boundary
+  p.o_partial = o_partial; p.m_partial = m_partial; p.l_partial = l_partial;
+  p.num_splits = 1; p.force_partial = 1;
+  p.token_lo = token_lo; p.token_hi = token_hi;
+  return launch_decode_stream(p, workspace, workspace_bytes, token_hi - token_lo,
+                              static_cast<cudaStream_t>(stream), variant >= 40 ? variant - 40 : 0);
+}
+
 extern "C" int bkv_decode_range_sm100(const void* q, int64_t q_batch_stride, int q_dtype,
                                       const void* cache, int64_t num_pages,
                                       int64_t page_stride_i32, int block_size, int heads_kv,

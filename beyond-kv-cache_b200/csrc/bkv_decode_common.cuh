@@ -67,6 +67,8 @@ __device__ __forceinline__ float load_v_level(const DecodeParams& p, int head, i
 int launch_decode_scalar(const DecodeParams& p, cudaStream_t stream);
 int launch_decode_mma(const DecodeParams& p, cudaStream_t stream, int config);
 int read_decode_status();
+int launch_combine_packed(const float* records, int num_splits, int64_t rows, void* out, int out_dtype,
+                          float* out_f32, cudaStream_t stream);
 int launch_decode_stream(const DecodeParams& p, void* workspace, int64_t workspace_bytes, int max_seq_len,
                          cudaStream_t stream, int config);
 int64_t stream_workspace_bytes();

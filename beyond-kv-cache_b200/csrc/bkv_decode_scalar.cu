@@ -149,11 +149,39 @@ __global__ void __launch_bounds__(kScalarWarps * 32) decode_scalar_kernel(const 
 }
 
 // One CTA of 128 threads merges the splits of one (request, query head) row.
-__global__ void __launch_bounds__(kHeadDim) combine_kernel(const float* __restrict__ o_partial,
-                                                           const float* __restrict__ m_partial,
-                                                           const float* __restrict__ l_partial,
-                                                           int num_splits, int64_t rows, void* out,
-                                                           int out_dtype, float* out_f32) {
+__global__ void __launch_bounds__(kHeadDim) combine_strided_kernel(const float* __restrict__ o_partial,
+                                                                   const float* __restrict__ m_partial,
+                                                                   const float* __restrict__ l_partial,
+                                                                   int num_splits, int64_t rows, int64_t split_stride,
+                                                                   void* out, int out_dtype, float* out_f32) {
+  // split s: o at o_partial + s*split_stride (rows x 128), m and l at m/l_partial + s*split_stride
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int d = threadIdx.x;
+  float M = -CUDART_INF_F;
+  for (int s = 0; s < num_splits; ++s)
+    if (l_partial[s * split_stride + row] > 0.f) M = fmaxf(M, m_partial[s * split_stride + row]);
+  float den = 0.f, num = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float ls = l_partial[s * split_stride + row];
+    const float w = ls > 0.f ? __expf(m_partial[s * split_stride + row] - M) : 0.f;
+    den += w * ls;
+    num += w * o_partial[s * split_stride + row * kHeadDim + d];
+  }
+  const float o = den > 0.f ? num / den : 0.f;
+  store_out(out, row * kHeadDim + d, out_dtype, o);
+  if (out_f32) out_f32[row * kHeadDim + d] = o;
+}
+
+}  // namespace
+
+// Dense partials ([splits][rows][128], [splits][rows], [splits][rows]) have split strides of
+// rows*128 and rows elements; a packed per-rank record (o | m | l) has one stride for all three.
+__global__ void __launch_bounds__(kHeadDim) combine_dense_kernel(const float* __restrict__ o_partial,
+                                                                 const float* __restrict__ m_partial,
+                                                                 const float* __restrict__ l_partial,
+                                                                 int num_splits, int64_t rows, void* out,
+                                                                 int out_dtype, float* out_f32) {
   pdl_wait();
   const int64_t row = blockIdx.x;
   const int d = threadIdx.x;
@@ -172,15 +200,23 @@ __global__ void __launch_bounds__(kHeadDim) combine_kernel(const float* __restri
   if (out_f32) out_f32[row * kHeadDim + d] = o;
 }
 
-}  // namespace
-
 int launch_combine(const float* o_partial, const float* m_partial, const float* l_partial,
                    int num_splits, int64_t rows, void* out, int out_dtype, float* out_f32,
                    cudaStream_t stream) {
   if (rows <= 0) return BKV_OK;
-  combine_kernel<<<static_cast<unsigned>(rows), kHeadDim, 0, stream>>>(
+  combine_dense_kernel<<<static_cast<unsigned>(rows), kHeadDim, 0, stream>>>(
       o_partial, m_partial, l_partial, num_splits, rows, out, out_dtype, out_f32);
   return check_launch("bkv_combine_sm100");
+}
+
+int launch_combine_packed(const float* records, int num_splits, int64_t rows, void* out, int out_dtype,
+                          float* out_f32, cudaStream_t stream) {
+  if (rows <= 0) return BKV_OK;
+  const int64_t stride = rows * (kHeadDim + 2);  // one record: o (rows x 128) | m (rows) | l (rows)
+  combine_strided_kernel<<<static_cast<unsigned>(rows), kHeadDim, 0, stream>>>(
+      records, records + rows * kHeadDim, records + rows * (kHeadDim + 1), num_splits, rows, stride, out, out_dtype,
+      out_f32);
+  return check_launch("bkv_combine_packed_sm100");
 }
 
 int launch_decode_scalar(const DecodeParams& p, cudaStream_t stream) {

@@ -196,8 +196,16 @@ __global__ void __maxnreg__(max_regs_for(NW))
     if (prefix[b + 1] != prefix[b]) continue;
     const int64_t row0 = static_cast<int64_t>(b) * p.heads_q * kHeadDim;
     for (int i = tid; i < p.heads_q * kHeadDim; i += NW * 32) {
-      store_out(p.out, row0 + i, p.out_dtype, 0.f);
-      if (p.out_f32) p.out_f32[row0 + i] = 0.f;
+      if (p.force_partial) {
+        p.o_partial[row0 + i] = 0.f;
+        if ((i & (kHeadDim - 1)) == 0) {
+          p.m_partial[(row0 + i) / kHeadDim] = -CUDART_INF_F;
+          p.l_partial[(row0 + i) / kHeadDim] = 0.f;
+        }
+      } else {
+        store_out(p.out, row0 + i, p.out_dtype, 0.f);
+        if (p.out_f32) p.out_f32[row0 + i] = 0.f;
+      }
     }
   }
   const int64_t G = static_cast<int64_t>(p.heads_kv * quads) * Tb;
@@ -417,7 +425,12 @@ __global__ void __maxnreg__(max_regs_for(NW))
       }
     }
     __syncthreads();
-    if (!work) continue;
+
+    // One request covers this CTA's whole share (few, long requests): the warps do not leave a
+    // partial each; they merge in shared memory and the CTA leaves one, so a request's chain of
+    // partials has one link per CTA instead of one per warp.  (CTA-uniform.)
+    int solo_b = request_of(first);
+    const bool solo = prefix[solo_b + 1] >= first + span;
 
     // ---- attention state of the request being streamed ------------------------------------
     uint32_t qb[2][4][2];  // B operand of QK: q of head hcol, pre-scaled by softmax_scale * log2(e)
@@ -580,9 +593,9 @@ __global__ void __maxnreg__(max_regs_for(NW))
 
     // ---- stream through the run, request by request ----------------------------------------
     int x = wa;
-    int b = request_of(wa);
+    int b = work ? request_of(wa) : 0;
     int run_done = 0;  // tiles of this run consumed so far
-    while (run_done < total && !dead) {
+    while (work && run_done < total && !dead) {
       while (prefix[b + 1] <= x) ++b;
       const int pb = prefix[b];
       const int nb = prefix[b + 1] - pb;
@@ -671,6 +684,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
         }
       }
       if (dead) break;
+      if (solo) break;  // the only request of this run: merged with the other warps below
 
       // ---- leave request b: final output or a partial ---------------------------------------
       float l_tot = l_run;  // tokens were spread over gid
@@ -679,7 +693,24 @@ __global__ void __maxnreg__(max_regs_for(NW))
       l_tot += __shfl_xor_sync(kFull, l_tot, 16);
       const bool whole = k0 == 0 && kend == nb;
       if (tig < nh) {
-        if (whole) {
+        if (whole && p.force_partial) {  // the caller merges across ranks: un-normalised (o, m, l)
+          const int64_t row = static_cast<int64_t>(b) * p.heads_q + hq0 + tig;
+          float2* dst = reinterpret_cast<float2*>(p.o_partial + row * kHeadDim);
+#pragma unroll
+          for (int P = 0; P < 2; ++P)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int d = 32 * (2 * vsel + P) + 8 * vu + 2 * i;
+              const float mn = vsel ? cmin[P][1] : cmin[P][0];
+              dst[d >> 1] = l_tot > 0.f ? make_float2((vsel ? oacc[P][i][1] : oacc[P][i][0]) + mn,
+                                                      (vsel ? oacc[P][i][3] : oacc[P][i][2]) + mn)
+                                        : make_float2(0.f, 0.f);
+            }
+          if (gid == 0) {
+            p.m_partial[row] = l_tot > 0.f ? m_used * kLn2 : -CUDART_INF_F;
+            p.l_partial[row] = l_tot;
+          }
+        } else if (whole) {
           const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
           const int64_t row = static_cast<int64_t>(b) * p.heads_q + hq0 + tig;
 #pragma unroll
@@ -719,6 +750,78 @@ __global__ void __maxnreg__(max_regs_for(NW))
         sp.ws_hdr[2 * range + (k0 > 0 ? 0 : 1)] = ((vh * B + b) << 1) | (kend == nb ? 1 : 0);
       x += kend - k0;
     }
+
+    if (solo) {
+      // ---- merge the warps of the CTA (all of them worked on request solo_b) ------------------
+      __syncthreads();  // every tile of every warp has been consumed: the rings are free
+      float* const mo = reinterpret_cast<float*>(gptr(kRingLoS));  // [NW][4][128]
+      float* const mm = mo + NW * 4 * kHeadDim;
+      float* const ml = mm + NW * 4;
+      const bool mine = work && !dead;
+      float l_tot = mine ? l_run : 0.f;  // tokens were spread over gid
+      l_tot += __shfl_xor_sync(kFull, l_tot, 4);
+      l_tot += __shfl_xor_sync(kFull, l_tot, 8);
+      l_tot += __shfl_xor_sync(kFull, l_tot, 16);
+      if (mine) {
+        float2* dst = reinterpret_cast<float2*>(mo + (warp * 4 + tig) * kHeadDim);
+#pragma unroll
+        for (int P = 0; P < 2; ++P)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int d = 32 * (2 * vsel + P) + 8 * vu + 2 * i;
+            const float mn = vsel ? cmin[P][1] : cmin[P][0];
+            dst[d >> 1] = make_float2((vsel ? oacc[P][i][1] : oacc[P][i][0]) + mn,
+                                      (vsel ? oacc[P][i][3] : oacc[P][i][2]) + mn);
+          }
+      }
+      if (gid == 0) {
+        mm[warp * 4 + tig] = mine ? m_used : -CUDART_INF_F;
+        ml[warp * 4 + tig] = l_tot;
+      }
+      __syncthreads();
+      const int k0c = first - prefix[solo_b];
+      const bool ends = first + span == prefix[solo_b + 1];
+      const bool whole = k0c == 0 && ends;
+      const int slot = 2 * ((cta * 2 + ph) * NW) + (k0c > 0 ? 0 : 1);  // of the CTA's first range
+      for (int idx = tid; idx < 4 * kHeadDim; idx += NW * 32) {
+        const int h = idx >> 7, d = idx & (kHeadDim - 1);
+        if (h >= nh) continue;
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < NW; ++w)
+          if (ml[w * 4 + h] > 0.f) M = fmaxf(M, mm[w * 4 + h]);
+        float den = 0.f, num = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+          const float lw = ml[w * 4 + h];
+          if (!(lw > 0.f)) continue;
+          const float wt = exp2f(mm[w * 4 + h] - M);
+          den += wt * lw;
+          num += wt * mo[(w * 4 + h) * kHeadDim + d];
+        }
+        const int64_t row = static_cast<int64_t>(solo_b) * p.heads_q + hq0 + h;
+        if (!whole) {
+          const int64_t prow = static_cast<int64_t>(slot) * 4 + h;
+          sp.ws_o[prow * kHeadDim + d] = num;
+          if (d == 0) {
+            sp.ws_m[prow] = M;
+            sp.ws_l[prow] = den;
+          }
+        } else if (p.force_partial) {
+          p.o_partial[row * kHeadDim + d] = den > 0.f ? num : 0.f;
+          if (d == 0) {
+            p.m_partial[row] = den > 0.f ? M * kLn2 : -CUDART_INF_F;
+            p.l_partial[row] = den;
+          }
+        } else {
+          const float o = den > 0.f ? num / den : 0.f;
+          store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
+          if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
+        }
+      }
+      if (!whole && tid == 0) sp.ws_hdr[slot] = ((vh * B + solo_b) << 1) | (ends ? 1 : 0);
+      __syncthreads();  // the scratch is ring space again
+    }
   }
 
   if (LOADER == 1) cp_async_wait_group<0>();
@@ -754,6 +857,7 @@ __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamP
   __shared__ int s_hdr[4][kFixGroup];
   __shared__ int s_list[4][kFixGroup];
   __shared__ int s_cnt[4], s_done[4];
+  __shared__ float s_red[3][4][4][kFixGroup];  // [M, num, den][group][head][dim]: cooperative mode only
   const int tid = threadIdx.x, g = tid >> 7, d = tid & (kFixGroup - 1);
   const int r0 = blockIdx.x * ranges_per_cta;
   if (tid < 32) {  // ranges_per_cta <= 32
@@ -765,7 +869,11 @@ __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamP
   __syncthreads();
   const int nown = s_nown;
   const int gqa = p.heads_q / p.heads_kv;
-  for (int oi = g; oi < nown; oi += 4) {
+  // One owner in this CTA (few, long requests): all four groups share its chain, group g taking
+  // every fourth part, and the four results are merged through shared memory.  Several owners:
+  // one group per owner.
+  const bool coop = nown == 1;
+  for (int oi = coop ? 0 : g; oi < nown; oi += 4) {
     const int range = s_owner[oi];
     const int hd = sp.ws_hdr[2 * range + 1];
     const int item = hd >> 1;
@@ -788,7 +896,7 @@ __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamP
       den[h] = den[h] * a + l2 * w;
       M[h] = Mn;
     };
-    auto merge_slot = [&](const int64_t slot0, const int64_t slot1, const int64_t slot2, const int64_t slot3, int n) {
+    auto merge_slots = [&](const int64_t slot0, const int64_t slot1, const int64_t slot2, const int64_t slot3, int n) {
       const int64_t slots[kFixBatch] = {slot0, slot1, slot2, slot3};
       float m2[kFixBatch][4], l2[kFixBatch][4], o2[kFixBatch][4];
 #pragma unroll
@@ -806,7 +914,7 @@ __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamP
 #pragma unroll
         for (int h = 0; h < 4; ++h) merge(h, m2[u][h], l2[u][h], o2[u][h]);
     };
-    merge_slot(2ll * range + 1, 0, 0, 0, 1);
+    if (!coop || g == 0) merge_slots(2ll * range + 1, 0, 0, 0, 1);
     const bool chain_open = (hd & 1) == 0;
     for (int base = range + 1; chain_open && base < num_ranges; base += kFixGroup) {
       const int r = base + d;
@@ -826,22 +934,58 @@ __global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamP
       }
       group_sync(g);
       const int cnt = s_cnt[g];
-      for (int c0 = 0; c0 < cnt; c0 += kFixBatch) {
+      const int first = coop ? g * kFixBatch : 0, stride = coop ? 4 * kFixBatch : kFixBatch;
+      for (int c0 = first; c0 < cnt; c0 += stride) {
         const int n = min(kFixBatch, cnt - c0);
-        merge_slot(2ll * s_list[g][c0], 2ll * s_list[g][min(c0 + 1, cnt - 1)], 2ll * s_list[g][min(c0 + 2, cnt - 1)],
-                   2ll * s_list[g][min(c0 + 3, cnt - 1)], n);
+        merge_slots(2ll * s_list[g][c0], 2ll * s_list[g][min(c0 + 1, cnt - 1)], 2ll * s_list[g][min(c0 + 2, cnt - 1)],
+                    2ll * s_list[g][min(c0 + 3, cnt - 1)], n);
       }
       const int done = s_done[g];
       group_sync(g);
       if (done) break;
     }
+    if (coop) {  // fold the four groups' results (uniform over the CTA: one owner)
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        s_red[0][g][h][d] = M[h];
+        s_red[1][g][h][d] = num[h];
+        s_red[2][g][h][d] = den[h];
+      }
+      __syncthreads();
+      if (g != 0) continue;
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        M[h] = -CUDART_INF_F;
+        num[h] = 0.f;
+        den[h] = 0.f;
+#pragma unroll
+        for (int gg = 0; gg < 4; ++gg) {
+          const float m2 = s_red[0][gg][h][d], l2 = s_red[2][gg][h][d], o2 = s_red[1][gg][h][d];
+          if (!(l2 > 0.f)) continue;
+          const float Mn = fmaxf(M[h], m2);
+          const float a = (M[h] == -CUDART_INF_F) ? 0.f : exp2f(M[h] - Mn);
+          const float w = exp2f(m2 - Mn);
+          num[h] = num[h] * a + o2 * w;
+          den[h] = den[h] * a + l2 * w;
+          M[h] = Mn;
+        }
+      }
+    }
 #pragma unroll
     for (int h = 0; h < 4; ++h) {
       if (h >= nh) continue;
-      const float o = den[h] > 0.f ? num[h] / den[h] : 0.f;
       const int64_t row = static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4 + h;
-      store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
-      if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
+      if (p.force_partial) {
+        p.o_partial[row * kHeadDim + d] = den[h] > 0.f ? num[h] : 0.f;
+        if (d == 0) {
+          p.m_partial[row] = den[h] > 0.f ? M[h] * kLn2 : -CUDART_INF_F;
+          p.l_partial[row] = den[h];
+        }
+      } else {
+        const float o = den[h] > 0.f ? num[h] / den[h] : 0.f;
+        store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
+        if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
+      }
     }
   }
 }

@@ -59,6 +59,22 @@ def gather_partials(o: torch.Tensor, m: torch.Tensor, l: torch.Tensor, group=Non
     return out[:, :, :d].contiguous(), out[:, :, d].contiguous(), out[:, :, d + 1].contiguous()
 
 
+_WORKSPACES: dict = {}
+
+
+def _stream_workspace(device: torch.device) -> torch.Tensor:
+    """Scratch of the persistent schedule, one per device, allocated on first use (calls on
+    one device are issued on one stream here, so they never overlap)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        with torch.cuda.device(device):
+            nbytes = int(_lib.load().bkv_decode_stream_workspace_bytes())
+        ws = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
 def decode_range_partial(
     q: torch.Tensor,
     cache: torch.Tensor,
@@ -84,6 +100,20 @@ def decode_range_partial(
     if q_points_k.dtype != q_points_v.dtype:
         q_points_k, q_points_v = q_points_k.float(), q_points_v.float()
     stat = stat_dtype if stat_dtype is not None else q.dtype
+    if batch <= 16384 and int(cache.shape[0]) <= (1 << 26) and layout.block_size in (16, 32, 64, 128):
+        # persistent schedule: every SM works on the range even when it is one request's
+        _lib.call(
+            "bkv_decode_range_stream_sm100",
+            q.data_ptr(), q.stride(0), _lib.dtype_code(q.dtype),
+            cache.data_ptr(), int(cache.shape[0]), int(cache.stride(0)), int(layout.block_size),
+            int(layout.num_kv_heads), _lib.dtype_code(stat),
+            block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
+            q_points_k.contiguous().data_ptr(), q_points_v.contiguous().data_ptr(), _lib.dtype_code(q_points_k.dtype),
+            o.data_ptr(), m.data_ptr(), l.data_ptr(), _stream_workspace(q.device).data_ptr(),
+            int(_stream_workspace(q.device).numel()), batch, heads_q, int(token_lo), int(token_hi),
+            float(softmax_scale), 0, 0, _lib.current_stream(q.device),
+        )
+        return o, m, l
     _lib.call(
         "bkv_decode_range_sm100",
         q.data_ptr(), q.stride(0), _lib.dtype_code(q.dtype),
@@ -114,19 +144,41 @@ def decode_kv_range_split(
     group=None,
 ) -> torch.Tensor:
     """Decode attention of a batch whose KV positions are split across the ranks of
-    ``group``: this rank attends ``[token_lo, token_hi)`` from its own pages, the partials
-    are all-gathered (NCCL over NVLink) and merged on every rank into ``out``
-    ``(batch, heads_q, 128)``.  ``q`` must be identical on all ranks."""
-    o, m, l = decode_range_partial(
-        q, cache, layout, block_table, seq_lens, q_points_k, q_points_v,
-        token_lo=token_lo, token_hi=token_hi, softmax_scale=softmax_scale, stat_dtype=stat_dtype,
-    )
-    if dist.is_initialized() and dist.get_world_size(group) > 1:
-        o_all, m_all, l_all = gather_partials(o, m, l, group)
-    else:
-        o_all, m_all, l_all = o.unsqueeze(0), m.unsqueeze(0), l.unsqueeze(0)
+    ``group``: this rank attends ``[token_lo, token_hi)`` from its own pages and leaves one
+    packed record ``o | m | l`` (rows x 130 float32); the records are all-gathered in ONE
+    collective (NCCL over NVLink) and merged on every rank into ``out``
+    ``(batch, heads_q, 128)``.  ``q`` must be identical on all ranks.  Buffers are kept per
+    (device, rows, world), so steady-state calls allocate nothing."""
+    batch, heads_q = int(q.shape[0]), int(q.shape[1])
+    rows = batch * heads_q
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    key = (q.device.type, q.device.index, rows, world)
+    bufs = _RECORDS.get(key)
+    if bufs is None:
+        rec = torch.empty((rows * 130,), dtype=torch.float32, device=q.device)
+        every = torch.empty((world * rows * 130,), dtype=torch.float32, device=q.device) if world > 1 else rec
+        bufs = _RECORDS[key] = (rec, every)
+    rec, every = bufs
+    o, m, l = rec[: rows * 128].view(rows, 128), rec[rows * 128 : rows * 129], rec[rows * 129 :]
+    if q_points_k.dtype != q_points_v.dtype:
+        q_points_k, q_points_v = q_points_k.float(), q_points_v.float()
+    stat = stat_dtype if stat_dtype is not None else q.dtype
+    ws = _stream_workspace(q.device)
     _lib.call(
-        "bkv_combine_sm100", o_all.data_ptr(), m_all.data_ptr(), l_all.data_ptr(), int(o_all.shape[0]),
-        int(o_all.shape[1]), out.data_ptr(), _lib.dtype_code(out.dtype), None, _lib.current_stream(q.device),
+        "bkv_decode_range_stream_sm100",
+        q.data_ptr(), q.stride(0), _lib.dtype_code(q.dtype),
+        cache.data_ptr(), int(cache.shape[0]), int(cache.stride(0)), int(layout.block_size),
+        int(layout.num_kv_heads), _lib.dtype_code(stat),
+        block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
+        q_points_k.contiguous().data_ptr(), q_points_v.contiguous().data_ptr(), _lib.dtype_code(q_points_k.dtype),
+        o.data_ptr(), m.data_ptr(), l.data_ptr(), ws.data_ptr(), int(ws.numel()), batch, heads_q,
+        int(token_lo), int(token_hi), float(softmax_scale), 0, 0, _lib.current_stream(q.device),
     )
+    if world > 1:
+        dist.all_gather_into_tensor(every, rec, group=group)  # rank-major records
+    _lib.call("bkv_combine_packed_sm100", every.data_ptr(), world, rows, out.data_ptr(), _lib.dtype_code(out.dtype),
+              None, _lib.current_stream(q.device))
     return out
+
+
+_RECORDS: dict = {}

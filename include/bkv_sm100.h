@@ -152,6 +152,32 @@ int bkv_decode_stream_sm100(const void* q, int64_t q_batch_stride, int q_dtype, 
                             float softmax_scale, int flags, int variant, bkv_stream_t stream);
 
 /*
+ * bkv_combine_sm100 over packed records: split s is the block of rows*130 floats at
+ * records + s*rows*130 laid out as o (rows x 128) | m (rows) | l (rows) - the form in which
+ * one rank's partials travel in a single all-gather (no counterpart in the reference).
+ */
+int bkv_combine_packed_sm100(const float* records, int num_splits, int64_t rows, void* out,
+                             int out_dtype, float* out_f32, bkv_stream_t stream);
+
+/*
+ * bkv_decode_range_sm100 under the persistent schedule of bkv_decode_stream_sm100: the
+ * un-normalised partials (o, m natural-log, l) of every (request, query head) over the
+ * positions [token_lo, min(token_hi, seq_len)), with all SMs busy even for one request
+ * (the range call above runs one CTA per request and head).  No counterpart in the
+ * reference, which has no KV-range sharding.  workspace as for bkv_decode_stream_sm100;
+ * token_lo must be a multiple of block_size.
+ */
+int bkv_decode_range_stream_sm100(const void* q, int64_t q_batch_stride, int q_dtype,
+                                  const void* cache, int64_t num_pages, int64_t page_stride_i32,
+                                  int block_size, int heads_kv, int stat_dtype,
+                                  const int32_t* block_table, int64_t block_table_stride,
+                                  const int32_t* seq_lens, const void* lvl_k, const void* lvl_v,
+                                  int table_dtype, float* o_partial, float* m_partial,
+                                  float* l_partial, void* workspace, int64_t workspace_bytes,
+                                  int batch, int heads_q, int token_lo, int token_hi,
+                                  float softmax_scale, int flags, int variant, bkv_stream_t stream);
+
+/*
  * bkv_decode_sm100 for callers that cannot allocate device memory (no counterpart in
  * the reference, whose launcher always receives a caller-allocated workspace).
  *

@@ -196,6 +196,38 @@ def test_kv_range_partials_merge_to_full():
     assert not (l[1].cpu().numpy()[~live] != 0).any()
 
 
+def test_kv_range_partials_under_the_persistent_schedule():
+    """parallel.decode_range_partial (bkv_decode_range_stream_sm100) over disjoint token ranges,
+    one of them a single very long request cut into many parts, + bkv_combine_sm100 == full
+    decode; empty ranges give (0, -inf, 0)."""
+    from beyond_kv_cache_b200 import parallel
+
+    lens = [9000, 130, 0, 64]
+    lk, tk, lv, tv = tables(2, 8)
+    cache, bt = oracle_cache(lens, 2, 16, "bf16", 10, tk.float().numpy(), tv.float().numpy())
+    q = torch.from_numpy(np.random.default_rng(4).standard_normal((4, 8, 128)).astype(np.float32)).to(torch.bfloat16)
+    want = oracle.decode_attention(q.float().numpy(), cache, oracle.PageGeometry(16, 2), bt, lens,
+                                   levels_k=lk.float().numpy(), levels_v=lv.float().numpy(),
+                                   softmax_scale=synth.softmax_scale(), stat="bf16")
+    layout = PagedLayout.build_hnd(16, 2, 128, 4, 32, 32)
+    qd, cd, btd = q.to(DEV), torch.from_numpy(cache).to(DEV), torch.from_numpy(bt).to(DEV)
+    lens_d = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    ranges = [(0, 48), (48, 4096), (4096, 16384)]
+    parts = [parallel.decode_range_partial(qd, cd, layout, btd, lens_d, lk.to(DEV), lv.to(DEV), token_lo=lo, token_hi=hi,
+                                           softmax_scale=synth.softmax_scale(), stat_dtype=torch.bfloat16)
+             for lo, hi in ranges]
+    o = torch.stack([p[0] for p in parts]).contiguous()
+    m = torch.stack([p[1] for p in parts]).contiguous()
+    l = torch.stack([p[2] for p in parts]).contiguous()
+    out = torch.empty((4, 8, 128), dtype=torch.float32, device=DEV)
+    _lib.call("bkv_combine_sm100", o.data_ptr(), m.data_ptr(), l.data_ptr(), len(ranges), 32, out.data_ptr(),
+              _lib.BKV_F32, None, _lib.current_stream(qd.device))
+    torch.cuda.synchronize()
+    assert np.abs(out.cpu().numpy() - want).max() <= TOL
+    assert not l[2][8:].any() and not o[2][8:].any()  # only request 0 reaches beyond 4096
+    assert bool(torch.isinf(m[2][8:]).all())
+
+
 def test_launcher_rejects_bad_contracts():
     from beyond_kv_cache_b200.quant.fa4_cute import beyond_mixed_decode_runtime as rt
 
