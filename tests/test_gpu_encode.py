@@ -95,11 +95,13 @@ def test_config0_cache_checksum(golden):
 
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
-@pytest.mark.parametrize("tokens,heads,shared", [(8, 2, True), (513, 8, False), (1, 4, False)])
+@pytest.mark.parametrize("tokens,heads,shared", [(8, 2, True), (513, 8, False), (1, 4, False), (40, 40, False),
+                                                 (20000, 8, False)])
 def test_writer_matches_oracle_random(tokens, heads, shared, kind):
     rng = np.random.default_rng(2708 + tokens)
     dt = KIND_TO_DTYPE[kind]
-    bs, pages = 64, 12
+    bs = 64
+    pages = max(12, tokens // bs + 2)
     geo = oracle.PageGeometry(bs, heads, 128)
     seed_pages = rng.integers(-(2**31), 2**31, (pages, geo.block_i32)).astype(np.int32)
     k = torch.from_numpy(rng.standard_normal((tokens, heads, 128)).astype(np.float32)).to(dt)
