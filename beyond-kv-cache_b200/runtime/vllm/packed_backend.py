@@ -91,6 +91,10 @@ class BeyondPackedBackend:
         return BeyondPackedImpl
 
     @staticmethod
+    def get_builder_cls():
+        return BeyondPackedMetadataBuilder
+
+    @staticmethod
     def get_supported_kernel_block_sizes() -> list[int]:
         return list(BEYOND_PACKED_BLOCK_SIZES)
 
@@ -103,6 +107,66 @@ class BeyondPackedBackend:
         if int(block_size) not in BEYOND_PACKED_BLOCK_SIZES:
             raise ValueError(f"packed cache block_size must be one of {BEYOND_PACKED_BLOCK_SIZES}")
         return (int(num_blocks), _paged_layout(block_size, num_kv_heads, head_size).block_i32)
+
+
+@dataclass
+class BeyondPackedMetadata:
+    """What ``BeyondPackedImpl.forward`` reads (reference `:3437, :3477-3516`): the device
+    tensors of vLLM's common attention metadata plus host mirrors of the per-request query
+    offsets and sequence lengths, so that classifying the batch costs no device read."""
+
+    num_actual_tokens: int
+    query_start_loc: torch.Tensor
+    seq_lens: torch.Tensor
+    block_table: torch.Tensor
+    slot_mapping: torch.Tensor
+    max_query_len: int
+    max_seq_len: int
+    _beyond_query_start_loc_list: Optional[list] = None
+    _beyond_seq_lens_list: Optional[list] = None
+
+
+class BeyondPackedMetadataBuilder:
+    """Builds :class:`BeyondPackedMetadata` from vLLM's ``CommonAttentionMetadata`` (reference
+    ``BeyondPackedMetadataBuilder.build`` / ``.build_for_cudagraph_capture``, `:4719-4828`).
+    The object is read by attribute name only, so any metadata carrying ``num_actual_tokens``,
+    ``query_start_loc[_cpu]``, ``seq_lens[_cpu]``, ``block_table_tensor``, ``slot_mapping``,
+    ``max_query_len`` and ``max_seq_len`` serves."""
+
+    def __init__(self, kv_cache_spec=None, layer_names=None, vllm_config=None, device=None):
+        self.kv_cache_spec = kv_cache_spec
+        self.layer_names = layer_names
+        self.vllm_config = vllm_config
+        self.device = device
+
+    @staticmethod
+    def _host_list(common, name: str, count: int):
+        mirror = getattr(common, f"{name}_cpu", None)
+        if mirror is None:
+            return None  # forward() falls back to one device read
+        return [int(v) for v in mirror[:count].tolist()]
+
+    def build(self, common_prefix_len: int, common_attn_metadata, fast_build: bool = False) -> BeyondPackedMetadata:
+        c = common_attn_metadata
+        num_reqs = int(getattr(c, "num_reqs", c.seq_lens.shape[0]))
+        block_table = getattr(c, "block_table_tensor", None)
+        if block_table is None:
+            block_table = c.block_table
+        return BeyondPackedMetadata(
+            num_actual_tokens=int(c.num_actual_tokens), query_start_loc=c.query_start_loc, seq_lens=c.seq_lens,
+            block_table=block_table, slot_mapping=c.slot_mapping, max_query_len=int(c.max_query_len),
+            max_seq_len=int(c.max_seq_len),
+            _beyond_query_start_loc_list=self._host_list(c, "query_start_loc", num_reqs + 1),
+            _beyond_seq_lens_list=self._host_list(c, "seq_lens", num_reqs))
+
+    def build_for_cudagraph_capture(self, common_attn_metadata) -> BeyondPackedMetadata:
+        """Capture-time metadata: every request is a one-token decode at the bucket's longest
+        context, whatever placeholder lengths the runner filled in (reference `:4790-4828`)."""
+        m = self.build(0, common_attn_metadata)
+        num_reqs = int(m.seq_lens.shape[0])
+        m._beyond_query_start_loc_list = list(range(num_reqs + 1))
+        m._beyond_seq_lens_list = [max(1, int(m.max_seq_len))] * num_reqs
+        return m
 
 
 class BeyondPackedImpl:

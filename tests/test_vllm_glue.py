@@ -1,0 +1,98 @@
+"""vLLM-facing glue on CPU: environment readers, the layout contract, the metadata builder
+and the registry wiring (against a stand-in for the vLLM modules it touches)."""
+
+import sys
+import types
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from beyond_kv_cache_b200.runtime.vllm import config, packed_backend, registration
+
+
+def test_env_readers(monkeypatch):
+    monkeypatch.setenv("X_INT", "12")
+    monkeypatch.setenv("X_BAD", "twelve")
+    assert config.env_int("X_INT", 3) == 12 and config.env_int("X_BAD", 3) == 3 and config.env_int("X_UNSET", 3) == 3
+    for word, want in (("Yes", True), ("off", False), ("enabled", True), ("none", False), ("maybe", True)):
+        monkeypatch.setenv("X_BOOL", word)
+        assert config.env_bool("X_BOOL", True) is want
+    assert config.env_bool("X_UNSET", False) is False
+    monkeypatch.setenv("X_BITS", "7")
+    with pytest.raises(ValueError, match="supports bits"):
+        config.env_bits("X_BITS")
+    monkeypatch.setenv("X_BITS", "4")
+    assert config.env_bits("X_BITS") == 4
+
+
+def test_real_packed_layout_contract():
+    config.validate_real_packed_layout(4, 32, 32)
+    with pytest.raises(NotImplementedError, match="only 4-bit"):
+        config.validate_real_packed_layout(5, 32, 32)
+    with pytest.raises(NotImplementedError, match="k_group_size"):
+        config.validate_real_packed_layout(4, 64, 32)
+    with pytest.raises(NotImplementedError, match="v_group_size"):
+        config.validate_real_packed_layout(4, 32, 16)
+
+
+def test_metadata_builder_mirrors_the_request_plan_on_the_host():
+    common = SimpleNamespace(
+        num_reqs=3, num_actual_tokens=3, max_query_len=1, max_seq_len=40,
+        query_start_loc=torch.tensor([0, 1, 2, 3], dtype=torch.int32), query_start_loc_cpu=torch.tensor([0, 1, 2, 3]),
+        seq_lens=torch.tensor([40, 7, 19], dtype=torch.int32), seq_lens_cpu=torch.tensor([40, 7, 19]),
+        block_table_tensor=torch.zeros((3, 3), dtype=torch.int32), slot_mapping=torch.tensor([39, 70, 118]))
+    builder = packed_backend.BeyondPackedBackend.get_builder_cls()()
+    m = builder.build(0, common)
+    assert m.num_actual_tokens == 3 and m._beyond_seq_lens_list == [40, 7, 19] and m._beyond_query_start_loc_list == [0, 1, 2, 3]
+    assert m.block_table is common.block_table_tensor and m.max_seq_len == 40
+    cap = builder.build_for_cudagraph_capture(common)
+    assert cap._beyond_seq_lens_list == [40, 40, 40] and cap._beyond_query_start_loc_list == [0, 1, 2, 3]
+    del common.seq_lens_cpu
+    assert builder.build(0, common)._beyond_seq_lens_list is None  # forward() then reads the device tensor
+
+
+def test_register_backend_without_a_registry_is_a_no_op(monkeypatch):
+    monkeypatch.setitem(sys.modules, "vllm.v1.attention.backends.registry", None)  # import fails
+    assert registration.register_backend() is False
+
+
+def test_register_backend_wires_registry_manager_and_spec(monkeypatch):
+    calls = {}
+
+    def mod(name, **attrs):
+        m = types.ModuleType(name)
+        m.__dict__.update(attrs)
+        monkeypatch.setitem(sys.modules, name, m)
+        return m
+
+    class FullAttentionManager:
+        pass
+
+    class Attention:
+        def __init__(self, name):
+            self.attn_backend = SimpleNamespace(get_name=lambda: name)
+            self.attn_type, self.num_kv_heads, self.head_size = "decoder", 8, 128
+
+        def get_kv_cache_spec(self, vllm_config):
+            return "stock"
+
+    manager_map = {}
+    for pkg in ("vllm", "vllm.v1", "vllm.v1.attention", "vllm.v1.attention.backends", "vllm.v1.core",
+                "vllm.model_executor", "vllm.model_executor.layers", "vllm.model_executor.layers.attention"):
+        mod(pkg)
+    mod("vllm.v1.attention.backends.registry", AttentionBackendEnum=SimpleNamespace(CUSTOM="CUSTOM"),
+        register_backend=lambda slot, qualname: calls.update(slot=slot, qualname=qualname))
+    mod("vllm.v1.core.single_type_kv_cache_manager", FullAttentionManager=FullAttentionManager, spec_manager_map=manager_map)
+    mod("vllm.model_executor.layers.attention.attention", Attention=Attention)
+    mod("vllm.v1.attention.backend", AttentionType=SimpleNamespace(DECODER="decoder"))
+
+    assert registration.register_backend() is True
+    assert calls["slot"] == "CUSTOM" and calls["qualname"].endswith("packed_backend.BeyondPackedBackend")
+    assert manager_map[packed_backend.BeyondPackedSpec] is FullAttentionManager
+    cfg = SimpleNamespace(cache_config=SimpleNamespace(block_size=16))
+    spec = Attention("CUSTOM").get_kv_cache_spec(cfg)
+    assert isinstance(spec, packed_backend.BeyondPackedSpec) and spec.real_page_size_bytes == 16 * 8 * 160
+    assert Attention("FLASH_ATTN").get_kv_cache_spec(cfg) == "stock"
+    patched = Attention.get_kv_cache_spec
+    assert registration.register_backend() is True and Attention.get_kv_cache_spec is patched  # idempotent
