@@ -6,18 +6,22 @@
 // may start in the middle of one request and end in the middle of another; the byte tables are
 // built once per CTA (twice when its share straddles two heads) instead of once per split.
 //
-// A warp keeps a private ring of tiles which it fills itself with bulk copies, running
-// STAGES tiles ahead across request boundaries, and a private online-softmax state; no block
-// barrier is executed while it works.  When it leaves a request it either
+// A warp keeps a private ring of tiles which it fills itself with asynchronous copies (16-byte
+// cp.async pieces or tensor copies, see LOADER), running STAGES tiles ahead across request
+// boundaries, and a private online-softmax state; no block barrier is executed while it works.
+// When it leaves a request it either
 //   * owns the whole request: normalises and writes the attention output, or
 //   * owns a part of it:      writes an un-normalised partial (o, m, l) into one of the two
 //     slots of its range (slot 0: the request began before the range, slot 1: it goes on
 //     behind it) together with a header word naming the request.
 // The fix-up kernel walks the ranges in order, collects the chain of partials of every
-// request that was cut, and merges them by log-sum-exp.
+// request that was cut, and merges them by log-sum-exp.  When one request covers a CTA's whole
+// share, its warps merge in shared memory first and the CTA leaves a single partial.
 //
-// Arithmetic and operand layouts (byte tables, group pairs, token permutations) are those of
-// bkv_decode_mma.cu with two changes that remove shuffles and shared-memory traffic:
+// Arithmetic and operand layouts (byte tables, group pairs) are those of bkv_decode_mma.cu with
+// three changes that remove shuffles, shared-memory traffic and padding:
+//   * tokens sit in natural order in the QK rows (row g / g+8 = token g / g+8) and as
+//     (t, t+4) pairs in the PV k-slots; the ring slot is swizzled instead of padded;
 //   * MMA column n stands for (query head n/2, group n%2 of the pair), so a lane's two QK
 //     accumulator columns are the two groups of ONE head and its scores need no exchange;
 //   * PV row g / g+8 of MMA i hold the even / odd dimension 8*(g%4)+2i(+1) of a group, so
@@ -438,8 +442,11 @@ __global__ void __maxnreg__(max_regs_for(NW))
     float oacc[2][4][4], cmin[2][4];
     float m_used = -CUDART_INF_F, l_run = 0.f;  // head tig
 
+    // `before_second` runs before the first read of the second tile (its wait), `after_first`
+    // after the last read of the first tile (its stage is refilled while the second tile is
+    // still being multiplied): the tile that was issued last gets the most time to arrive.
     auto process = [&](auto nt_tag, auto partial_tag, const uint32_t sbA, const uint32_t sbB, const int nvA,
-                       const int nvB) {
+                       const int nvB, auto&& before_second, auto&& after_first) {
       constexpr int NT = decltype(nt_tag)::value;
       constexpr bool PARTIAL = decltype(partial_tag)::value;
       const uint32_t sb[2] = {sbA, sbB};
@@ -448,6 +455,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
       float sacc[NT][2][4];
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
+        if (t == 1) before_second();
 #pragma unroll
         for (int P = 0; P < 2; ++P) {
           const uint32_t ka = sb[t] + (P ? kc_off1 : kc_off0);
@@ -588,6 +596,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
           const uint32_t ones = 0x3C003C00u;
           mma16816(cmin[P], ones, ones, ones, ones, mb2[0], mb2[1]);
         }
+        if (NT == 2 && t == 0) after_first();
       }
     };
 
@@ -644,34 +653,46 @@ __global__ void __maxnreg__(max_regs_for(NW))
         const int sB = s + 1 == STAGES ? 0 : s + 1;
         const uint32_t phaseB = s + 1 == STAGES ? phase ^ 1u : phase;
         // (the timing experiment stops issuing after the first fill and so stops waiting too)
-        if (LOADER == 1) {
-          if (n_done < n_issued && !nowait) {
-            cp_async_wait_pending(n_issued - n_done - cnt);  // this thread's pieces of the tile(s) ...
-            __syncwarp();                                     // ... and every other lane's
+        auto wait_tile = [&](int ahead, int stage, uint32_t parity) {  // tile n_done + ahead of this warp
+          if (n_done + ahead >= n_issued) return;
+          if (LOADER == 1) {
+            if (nowait) return;
+            cp_async_wait_pending(n_issued - n_done - ahead - 1);  // this thread's pieces of the tile ...
+            __syncwarp();                                           // ... and every other lane's
+          } else if (!wait_full(bar_base + 8 * stage, parity)) {
+            dead = true;
           }
-        } else {
-          if (n_done < n_issued && !wait_full(bar_base + 8 * s, phase)) { dead = true; break; }
-          if (cnt == 2 && n_done + 1 < n_issued && !wait_full(bar_base + 8 * sB, phaseB)) { dead = true; break; }
-        }
+        };
+        auto refill = [&](int ahead, int stage) {  // the stage of tile n_done + ahead is free again
+          if (noload) return;
+          __syncwarp();
+          if (LOADER != 1) fence_proxy_async();  // reads of the generic proxy before writes of the async proxy
+          if (run_done + ahead + STAGES < total) issue(run_done + ahead + STAGES, stage);
+        };
+        wait_tile(0, s, phase);
+        if (dead) break;
         const int rem = ntok - kTile * k;
         const int nvA = (bad_mask >> s) & 1 ? 0 : min(kTile, rem);
         const int nvB = cnt == 2 ? ((bad_mask >> sB) & 1 ? 0 : min(kTile, rem - kTile)) : 0;
         const uint32_t sbA = ring_base + s * kSlotBytes, sbB = ring_base + sB * kSlotBytes;
+        auto wait_second = [&] { wait_tile(1, sB, phaseB); };
+        auto refill_first = [&] { refill(0, s); };
+        auto nothing = [] {};
         if (cnt == 2) {
-          if (nvA == kTile && nvB == kTile)
-            process(std::integral_constant<int, 2>{}, std::false_type{}, sbA, sbB, nvA, nvB);
-          else if (nvA > 0 || nvB > 0)
-            process(std::integral_constant<int, 2>{}, std::true_type{}, sbA, sbB, nvA, nvB);
-        } else if (nvA > 0) {
-          process(std::integral_constant<int, 1>{}, std::true_type{}, sbA, sbA, nvA, 0);
+          if (nvA == kTile && nvB == kTile) {
+            process(std::integral_constant<int, 2>{}, std::false_type{}, sbA, sbB, nvA, nvB, wait_second, refill_first);
+          } else if (nvA > 0 || nvB > 0) {
+            process(std::integral_constant<int, 2>{}, std::true_type{}, sbA, sbB, nvA, nvB, wait_second, refill_first);
+          } else {  // two unmapped pages: nothing to compute, the ring still turns
+            wait_second();
+            refill_first();
+          }
+          refill(1, sB);
+        } else {
+          if (nvA > 0) process(std::integral_constant<int, 1>{}, std::true_type{}, sbA, sbA, nvA, 0, nothing, nothing);
+          refill(0, s);
         }
-        // the stages are free again: refill them with the tiles STAGES ahead
-        if (!noload) {
-          __syncwarp();
-          if (LOADER != 1) fence_proxy_async();  // reads of the generic proxy before writes of the async proxy
-          if (run_done + STAGES < total) issue(run_done + STAGES, s);
-          if (cnt == 2 && run_done + 1 + STAGES < total) issue(run_done + 1 + STAGES, sB);
-        }
+        if (dead) break;
         k += cnt;
         run_done += cnt;
         n_done += cnt;
