@@ -442,11 +442,11 @@ __global__ void __maxnreg__(max_regs_for(NW))
     float oacc[2][4][4], cmin[2][4];
     float m_used = -CUDART_INF_F, l_run = 0.f;  // head tig
 
-    // `before_second` runs before the first read of the second tile (its wait), `after_first`
-    // after the last read of the first tile (its stage is refilled while the second tile is
+    // `before_second` runs before the first read of the second tile (its wait), `after_reads(t)`
+    // after the last read of tile t from the ring (its stage is refilled while its V part is
     // still being multiplied): the tile that was issued last gets the most time to arrive.
     auto process = [&](auto nt_tag, auto partial_tag, const uint32_t sbA, const uint32_t sbB, const int nvA,
-                       const int nvB, auto&& before_second, auto&& after_first) {
+                       const int nvB, auto&& before_second, auto&& after_reads) {
       constexpr int NT = decltype(nt_tag)::value;
       constexpr bool PARTIAL = decltype(partial_tag)::value;
       const uint32_t sb[2] = {sbA, sbB};
@@ -554,9 +554,9 @@ __global__ void __maxnreg__(max_regs_for(NW))
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         const uint32_t sa0 = sb[t] + vs_off0, sa1 = sb[t] + vs_off1;
+        uint32_t wb2[2][2], mb2[2][2];  // [pair][k-slots 2tig.. / 2tig+8..]
 #pragma unroll
         for (int P = 0; P < 2; ++P) {
-          uint32_t wb2[2], mb2[2];
 #pragma unroll
           for (int o = 0; o < 2; ++o) {
             // statistic words of tokens tig+8o and tig+4+8o
@@ -578,9 +578,13 @@ __global__ void __maxnreg__(max_regs_for(NW))
               wv &= keep;
               mv &= keep;
             }
-            wb2[o] = wv;
-            mb2[o] = mv;
+            wb2[P][o] = wv;
+            mb2[P][o] = mv;
           }
+        }
+        after_reads(t);  // nothing of this tile is read from the ring any more
+#pragma unroll
+        for (int P = 0; P < 2; ++P) {
           const uint32_t vl = P ? vlane1 : vlane0;
           uint32_t av[4][4];
 #pragma unroll
@@ -592,11 +596,10 @@ __global__ void __maxnreg__(max_regs_for(NW))
             av[i][3] = lut_load(__byte_perm(vidx[t][P][1][1], vl, sel));
           }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) mma16816(oacc[P][i], av[i][0], av[i][1], av[i][2], av[i][3], wb2[0], wb2[1]);
+          for (int i = 0; i < 4; ++i) mma16816(oacc[P][i], av[i][0], av[i][1], av[i][2], av[i][3], wb2[P][0], wb2[P][1]);
           const uint32_t ones = 0x3C003C00u;
-          mma16816(cmin[P], ones, ones, ones, ones, mb2[0], mb2[1]);
+          mma16816(cmin[P], ones, ones, ones, ones, mb2[P][0], mb2[P][1]);
         }
-        if (NT == 2 && t == 0) after_first();
       }
     };
 
@@ -676,21 +679,21 @@ __global__ void __maxnreg__(max_regs_for(NW))
         const int nvB = cnt == 2 ? ((bad_mask >> sB) & 1 ? 0 : min(kTile, rem - kTile)) : 0;
         const uint32_t sbA = ring_base + s * kSlotBytes, sbB = ring_base + sB * kSlotBytes;
         auto wait_second = [&] { wait_tile(1, sB, phaseB); };
-        auto refill_first = [&] { refill(0, s); };
-        auto nothing = [] {};
+        auto refill_tile = [&](int t) { refill(t, t ? sB : s); };
         if (cnt == 2) {
           if (nvA == kTile && nvB == kTile) {
-            process(std::integral_constant<int, 2>{}, std::false_type{}, sbA, sbB, nvA, nvB, wait_second, refill_first);
+            process(std::integral_constant<int, 2>{}, std::false_type{}, sbA, sbB, nvA, nvB, wait_second, refill_tile);
           } else if (nvA > 0 || nvB > 0) {
-            process(std::integral_constant<int, 2>{}, std::true_type{}, sbA, sbB, nvA, nvB, wait_second, refill_first);
+            process(std::integral_constant<int, 2>{}, std::true_type{}, sbA, sbB, nvA, nvB, wait_second, refill_tile);
           } else {  // two unmapped pages: nothing to compute, the ring still turns
             wait_second();
-            refill_first();
+            refill_tile(0);
+            refill_tile(1);
           }
-          refill(1, sB);
+        } else if (nvA > 0) {
+          process(std::integral_constant<int, 1>{}, std::true_type{}, sbA, sbA, nvA, 0, [] {}, refill_tile);
         } else {
-          if (nvA > 0) process(std::integral_constant<int, 1>{}, std::true_type{}, sbA, sbA, nvA, 0, nothing, nothing);
-          refill(0, s);
+          refill_tile(0);
         }
         if (dead) break;
         k += cnt;
