@@ -34,8 +34,16 @@ static int mma_config() {
   static const int c = env_int("BKV_MMA_CONFIG");
   return c;
 }
+// Timing experiments (skip the loads, skip the waits, force a share policy).  Most of them make
+// the kernels compute on stale data, so they are honoured only when
+// BKV_TIMING_EXPERIMENTS=1 is set as well, and say so once on stderr.
 static int debug_flags() {
-  static const int f = env_int("BKV_DEBUG_FLAGS");
+  static const int f = [] {
+    const int flags = env_int("BKV_DEBUG_FLAGS");
+    if (flags == 0 || env_int("BKV_TIMING_EXPERIMENTS") != 1) return 0;
+    fprintf(stderr, "libbkv_sm100: BKV_DEBUG_FLAGS=0x%x - timing experiment, decode results are not valid\n", flags);
+    return flags;
+  }();
   return f;
 }
 

@@ -83,6 +83,7 @@ struct StreamParams {
   int* ws_prefix;  // [batch + 1] tiles before request b, written by stream_prefix_kernel when batch > kMaxBatch
   int quads;     // query-head quads per kv head
   int aligned;   // 1: every CTA's share lies inside one head (heads get floor or ceil of C / heads CTAs)
+  int straddle_tiles;  // equal shares: tiles by which a share that straddles two heads is shortened
 };
 
 // one box of the packed cache, seen as [page][64-byte row][64 bytes], into a ring slot
@@ -233,8 +234,25 @@ __global__ void __maxnreg__(max_regs_for(NW))
     ga = static_cast<int64_t>(h) * Tb + static_cast<int64_t>(Tb) * idx / cnt;
     gb = static_cast<int64_t>(h) * Tb + static_cast<int64_t>(Tb) * (idx + 1) / cnt;
   } else {
-    ga = G * cta / C;
-    gb = G * (cta + 1) / C;
+    // Equal shares of COST: a CTA whose share straddles two heads builds the tables twice and
+    // restarts its pipelines, which is worth `straddle_tiles` tiles.  The cost line is the tile
+    // line with a gap of that length at every head boundary; a share that contains a gap is
+    // that much shorter in tiles, one that ends inside a gap ends at the head boundary.
+    const int hv = p.heads_kv * quads;
+    const int64_t gap = sp.straddle_tiles;
+    const int64_t L = G + (hv - 1) * gap;
+    auto to_tile = [&](int64_t x) {
+      int64_t shift = 0;
+      for (int h = 1; h < hv; ++h) {
+        const int64_t start = static_cast<int64_t>(h) * Tb + (h - 1) * gap;
+        if (x >= start + gap) shift += gap;
+        else if (x > start) return static_cast<int64_t>(h) * Tb;
+        else break;
+      }
+      return x - shift;
+    };
+    ga = to_tile(L * cta / C);
+    gb = to_tile(L * (cta + 1) / C);
   }
 
   // ---- per-lane roles (see the file comment) ----------------------------------------------
@@ -1156,14 +1174,17 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   if (ctas > sm_count) ctas = sm_count;
   const int C = static_cast<int>(ctas);
   // Equal shares make the CTAs whose share straddles two heads build the tables twice and
-  // restart their pipelines (about 10 us on the critical path); head-aligned shares avoid that
-  // but the heads served by fewer CTAs finish later.  Take the cheaper of the two estimates
-  // (0.1 us per tile and SM).
+  // restart their pipelines (about 10 us, which the share computation takes off their tile
+  // count); head-aligned shares avoid that but the heads served by fewer CTAs finish later.
+  // Take the cheaper of the two estimates (0.1 us per tile and SM).
   {
     const int base = C / hv;
     const double per_cta_us = static_cast<double>(tiles_max) / C * 0.1;
     const double aligned_loss_us = per_cta_us * (static_cast<double>(C) / hv / base - 1.0);
-    sp.aligned = (C % hv == 0 || aligned_loss_us < 10.0) ? 1 : 0;
+    sp.straddle_tiles = 100;  // ~10 us
+    // compensated equal shares lose about (heads - 1) gaps spread over all CTAs
+    const double equal_loss_us = 10.0 * (hv - 1) / C + 1.0;
+    sp.aligned = (C % hv == 0 || aligned_loss_us < equal_loss_us) ? 1 : 0;
     if (p.flags & BKV_FLAG_DEBUG_EQUAL_SHARES) sp.aligned = 0;
     if (p.flags & BKV_FLAG_DEBUG_ALIGNED_SHARES) sp.aligned = 1;
   }
