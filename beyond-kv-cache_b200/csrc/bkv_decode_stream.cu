@@ -84,6 +84,7 @@ struct StreamParams {
   int quads;     // query-head quads per kv head
   int aligned;   // 1: every CTA's share lies inside one head (heads get floor or ceil of C / heads CTAs)
   int straddle_tiles;  // equal shares: tiles by which a share that straddles two heads is shortened
+  int q_vec;           // 16-bit queries whose rows can be read in 8-byte pieces
 };
 
 // one box of the packed cache, seen as [page][64-byte row][64 bytes], into a ring slot
@@ -330,6 +331,13 @@ __global__ void __maxnreg__(max_regs_for(NW))
     const int wb = first + static_cast<int>(static_cast<int64_t>(span) * (warp + 1) / NW);
     const int total = wb - wa;
     const bool work = total > 0 && !dead;
+    // this head's level tables: requested now, stored to shared memory after the first ring fill
+    // has been issued, so the read overlaps the page-id read below
+    float level_early = 0.f;
+    if (tid < 128) {
+      const int which = tid >> 6, g = (tid >> 4) & 3, c = tid & 15;
+      level_early = which ? load_v_level(p, head, g, c) : load_k_level(p, head, g, c);
+    }
 
     // cp.async loader: lane l moves the l-th 16 bytes of each 512-byte half of the K and V
     // codes (tokens 0-7 / 8-15); lanes 0-15 move the K statistics, lanes 16-31 the V statistics
@@ -423,13 +431,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
     }
 
     __syncthreads();  // the previous head's tables are no longer read
-    {                 // level tables -> fp16 in shared memory
-      __half* lv = reinterpret_cast<__half*>(gptr(kLevels));
-      for (int i = tid; i < 128; i += NW * 32) {
-        const int which = i >> 6, g = (i >> 4) & 3, c = i & 15;
-        lv[i] = __float2half_rn(which ? load_v_level(p, head, g, c) : load_k_level(p, head, g, c));
-      }
-    }
+    if (tid < 128) reinterpret_cast<__half*>(gptr(kLevels))[tid] = __float2half_rn(level_early);  // fp16 [K|V][4][16]
     __syncthreads();
     {  // byte -> (level[low nibble], level[high nibble]) tables, one copy per bank.
        // Block P (P = 0, 1) holds, in bank l, the K table of group 2*((l>>1)&1)+P and the
@@ -641,8 +643,19 @@ __global__ void __maxnreg__(max_regs_for(NW))
           for (int j = 0; j < 4; ++j) {
             const int d0 = 32 * (2 * ksel + P) + 16 * khalf + 4 * j;
             float f[4];
+            if (sp.q_vec) {
+              const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const unsigned short*>(p.q) + qoff + d0);
+              const uint32_t w[2] = {raw.x, raw.y};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) f[i] = live_h ? load_q(p.q, qoff + d0 + i, p.q_dtype) * p.scale_log2 : 0.f;
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t bits = (i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xFFFFu);
+                const float v = p.q_dtype == BKV_BF16 ? bf16_bits_to_f32(bits) : f16_bits_to_f32(bits);
+                f[i] = live_h ? v * p.scale_log2 : 0.f;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) f[i] = live_h ? load_q(p.q, qoff + d0 + i, p.q_dtype) * p.scale_log2 : 0.f;
+            }
             const uint32_t lo2 = pack_half2(f[0], f[1]), hi2 = pack_half2(f[2], f[3]);
             const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo2));
             const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&hi2));
@@ -1166,6 +1179,8 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   sp.d = p;
   const int gqa = p.heads_q / p.heads_kv;
   sp.quads = (gqa + 3) / 4;
+  sp.q_vec = (p.q_dtype == BKV_BF16 || p.q_dtype == BKV_F16) && reinterpret_cast<uintptr_t>(p.q) % 8 == 0 &&
+             p.q_batch_stride % 4 == 0;
   const int hv = p.heads_kv * sp.quads;
   if (hv > sm_count) return BKV_ERR_UNSUPPORTED;
   const int64_t tiles_max = static_cast<int64_t>(hv) * p.batch * ((max_seq_len + kTile - 1) / kTile);
@@ -1174,16 +1189,16 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   if (ctas > sm_count) ctas = sm_count;
   const int C = static_cast<int>(ctas);
   // Equal shares make the CTAs whose share straddles two heads build the tables twice and
-  // restart their pipelines (about 10 us, which the share computation takes off their tile
+  // restart their pipelines (a few us, which the share computation takes off their tile
   // count); head-aligned shares avoid that but the heads served by fewer CTAs finish later.
   // Take the cheaper of the two estimates (0.1 us per tile and SM).
   {
     const int base = C / hv;
     const double per_cta_us = static_cast<double>(tiles_max) / C * 0.1;
     const double aligned_loss_us = per_cta_us * (static_cast<double>(C) / hv / base - 1.0);
-    sp.straddle_tiles = 100;  // ~10 us
+    sp.straddle_tiles = 40;  // ~4 us: with 100 the straddling CTAs were measured to finish 7 us early
     // compensated equal shares lose about (heads - 1) gaps spread over all CTAs
-    const double equal_loss_us = 10.0 * (hv - 1) / C + 1.0;
+    const double equal_loss_us = 4.0 * (hv - 1) / C + 1.0;
     sp.aligned = (C % hv == 0 || aligned_loss_us < equal_loss_us) ? 1 : 0;
     if (p.flags & BKV_FLAG_DEBUG_EQUAL_SHARES) sp.aligned = 0;
     if (p.flags & BKV_FLAG_DEBUG_ALIGNED_SHARES) sp.aligned = 1;
@@ -1219,6 +1234,10 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
       set_last_cuda_error(e, "cudaFuncSetAttribute(decode_stream_kernel)");
       return BKV_ERR_CUDA;
     }
+    // the small kernels around the decode grid ask for the same shared-memory carve-out, so the
+    // SMs are not reconfigured between the launches of a step
+    cudaFuncSetAttribute(stream_fixup_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(stream_prefix_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured[p.stat_bf16 ? 1 : 0][dev] = true;
   }
   kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp, maps.map16, maps.map4, maps.mapvs);
