@@ -8,10 +8,11 @@
 namespace bkv {
 namespace mma {
 
-// ---- one 16-token tile of one KV head in a ring slot ---------------------------------
+// ---- one 16-token tile of one KV head in a ring slot of the split-grid kernel -------------
 // K codes (16 x 64 B), K statistics (16 x 16 B), V codes (16 x 64 B), V statistics
 // (4 groups x 16 tokens x 4 B).  The code rows of tokens 8-15 start kCodeSkew bytes later
 // than contiguous, which makes the per-lane code loads of the MMA layouts conflict-free.
+// (The persistent kernel uses a swizzled slot instead, see bkv_decode_stream.cu.)
 constexpr int kTile = 16;
 constexpr int kCodeSkew = 16;
 constexpr int kOffKLo = 0;
@@ -21,7 +22,6 @@ constexpr int kOffVLo = kOffKStat + 256;
 constexpr int kOffVHi = kOffVLo + 512 + kCodeSkew;
 constexpr int kOffVStat = kOffVHi + 512;
 constexpr int kTileBytes = kOffVStat + 256;  // 2592
-constexpr int kTilePayload = 2560;           // bytes the bulk copies of one tile deliver
 
 // ---- shared-memory map of a CTA that owns the SM ---------------------------------------
 constexpr uint32_t kSmemBase = 0x400;              // dynamic shared memory starts after the 1 KB the system reserves
@@ -45,9 +45,6 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -115,10 +112,6 @@ struct WaitBudget {
     }
     return now - start > kWaitLimitNs;
   }
-  __device__ __forceinline__ void reset() {
-    polls = 0;
-    start = 0;
-  }
 };
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -166,11 +159,6 @@ __device__ __forceinline__ uint32_t lut_load(uint32_t addr) {
 }
 // Ring loads are volatile: they stay, in program order, between the full-barrier wait of
 // their tile and the bulk copies that later refill the same ring stage.
-__device__ __forceinline__ uint4 ring_load128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
 template <int IMM>
 __device__ __forceinline__ uint4 ring_load128i(uint32_t addr) {
   uint4 v;
@@ -196,8 +184,6 @@ __device__ __forceinline__ float2 stat_word_to_f32(uint32_t w) {  // (scale, min
   if (BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
   return __half22float2(*reinterpret_cast<const __half2*>(&w));
 }
-// byte offset of token t's 64-byte code row inside a K or V code area of a tile
-__host__ __device__ constexpr int code_row_off(int t) { return t * 64 + (t >= 8 ? kCodeSkew : 0); }
 
 // registers a thread may use when one CTA of NW warps owns the SM: the register file is
 // split over the four schedulers (16 K registers each) and a CTA's warps are dealt to them
