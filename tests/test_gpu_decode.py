@@ -119,6 +119,17 @@ def test_persistent_schedule_cut_requests(bs, heads_kv, gqa, kind, variant):
     assert not out[3].any() and not out32[3].any()  # seq_len 0 -> zeros
 
 
+@pytest.mark.parametrize("variant", [40, 42])
+def test_persistent_schedule_many_heads_tiny_requests(variant):
+    """Sixteen KV heads and requests of one to three tiles: one CTA per head, shares shorter than
+    the straddle allowance, most warps without work."""
+    lens = [1, 17, 0, 40, 16]
+    lk, tk, lv, tv = tables(16, 13)
+    cache, bt = oracle_cache(lens, 16, 16, "f16", 21, tk.float().numpy(), tv.float().numpy())
+    q = torch.from_numpy(np.random.default_rng(8).standard_normal((len(lens), 32, 128)).astype(np.float32)).to(torch.float16)
+    _check(q, cache, bt, lens, 16, 16, lk, lv, "f16", variant=variant)
+
+
 def test_persistent_schedule_large_batch():
     """More requests than the in-kernel request table holds (1024): the prefix sums come
     from the planning kernel.  Short ragged requests, some empty."""
