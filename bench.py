@@ -72,6 +72,12 @@ def parse_args():
     ap.add_argument("--kv-split", action="store_true",
                     help="one 128K-token sequence whose KV range is split over the ranks (torchrun): per-rank "
                          "range decode, NCCL all-gather of the partials, log-sum-exp merge on every rank")
+    ap.add_argument("--box", action="store_true",
+                    help="whole-model decode: random-init Llama-3.1-8B (library GEMMs) with the packed attention "
+                         "backend in every layer, 4500 requests x 1024-token contexts + 128 generated tokens")
+    ap.add_argument("--box-batch", type=int, default=4500, help="requests over all GPUs (--box)")
+    ap.add_argument("--box-wave", type=int, default=2250, help="most requests resident on one GPU at a time (--box)")
+    ap.add_argument("--box-layers", type=int, default=32)
     ap.add_argument("--sweep", action="store_true",
                     help="context sweep 1K..128K at 4M KV tokens on one GPU, with the bf16-KV baselines")
     return ap.parse_args()
@@ -251,6 +257,14 @@ def main():
             dist.barrier()
             dist.destroy_process_group()
         return
+    if args.box:
+        line = measure_box(args, world, rank, local_rank, dev)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if args.serve:
         line = measure_serve(args, world, rank, local_rank, dev)
         if rank == 0:
@@ -344,6 +358,191 @@ def measure_kv_split(args, world, rank, local_rank, dev, ctx: int = 131072):
         "config": {"workload": f"one sequence x ctx {ctx}, {HEADS_Q} q / {HEADS_KV} kv heads, {BS}-token pages, "
                                f"KV range split over {world} GPU(s), NCCL all-gather of (o, m, l) + merge"},
         "data": "synthetic",
+    }
+
+
+def measure_box(args, world, rank, local_rank, dev, prompt: int = 1024, gen_steps: int = 128):
+    """Whole-model decode throughput.  A random-init Llama-3.1-8B-shaped decoder (hidden 4096,
+    32 / 8 heads, FFN 14336, vocabulary 128256, bf16 weights N(0, 0.02)) whose GEMMs, norms and
+    activation are plain torch library calls and whose attention is `BeyondPackedImpl.forward`
+    (encode-on-write + packed decode) with per-layer, per-head tables.  The `--box-batch`
+    requests are dealt to the ranks (weights replicated, no collective); a rank that cannot hold
+    its share at once runs it in waves.  The packed caches of the 1024-token contexts are filled
+    by the encode kernel from synthetic K/V rows (a prefill of a random-init model yields
+    equally arbitrary rows); the timed region is the `gen_steps` decode steps, each one CUDA
+    graph replay of the full model step including sampling (arg-max) and slot derivation."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from beyond_kv_cache_b200 import _lib, synth
+    from beyond_kv_cache_b200.quant.beyond_cute import PagedLayout, write_tokens_to_paged_cache
+    from beyond_kv_cache_b200.runtime.vllm.packed_backend import BeyondPackedImpl, BeyondPackedMetadata
+
+    LAYERS, HID, FFN, VOCAB, BS = args.box_layers, 4096, 14336, 128256, args.page
+    mine = len(range(rank, args.box_batch, world))
+    waves = max(1, -(-mine // args.box_wave))
+    batch = -(-mine // waves)  # requests resident per wave (the last wave is padded to the same shape)
+    layout = PagedLayout.build_hnd(BS, HEADS_KV, HEAD_DIM, 4, 32, 32)
+    pages_per_seq = -(-(prompt + gen_steps) // BS)
+    block_table, num_pages = synth.random_block_table(batch, pages_per_seq, seed=rank, device=dev)
+
+    def weight(*shape):
+        return torch.empty(shape, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.02)
+
+    torch.manual_seed(1234)  # the same replica on every rank
+    embed, lm_head, final_norm = weight(VOCAB, HID), weight(HID, VOCAB), torch.ones(HID, dtype=torch.bfloat16, device=dev)
+    layers = []
+    for li in range(LAYERS):
+        impl = BeyondPackedImpl(HEADS_Q, HEAD_DIM, synth.softmax_scale(), HEADS_KV)
+        lk, tk = (t.to(dev) for t in synth.make_tables(HEADS_KV, seed=li, which="k"))
+        lv, tv = (t.to(dev) for t in synth.make_tables(HEADS_KV, seed=li, which="v"))
+        impl.set_quant_tables(lk, tk, lv, tv)
+        layers.append({
+            "impl": impl, "tables": (lk, tk, lv, tv),
+            "wqkv": weight(HID, (HEADS_Q + 2 * HEADS_KV) * HEAD_DIM), "wo": weight(HEADS_Q * HEAD_DIM, HID),
+            "wgu": weight(HID, 2 * FFN), "wdown": weight(FFN, HID),
+            "n1": torch.ones(HID, dtype=torch.bfloat16, device=dev), "n2": torch.ones(HID, dtype=torch.bfloat16, device=dev),
+            "cache": torch.zeros((num_pages, layout.block_i32), dtype=torch.int32, device=dev),
+        })
+    inv_freq = 1.0 / (500000.0 ** (torch.arange(0, HEAD_DIM, 2, device=dev, dtype=torch.float32) / HEAD_DIM))
+    angles = torch.arange(pages_per_seq * BS, device=dev, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    rope_cos, rope_sin = angles.cos(), angles.sin()
+
+    def fill_caches(seed):
+        # contexts of `prompt` tokens: one synthetic block of rows, written request block by request block
+        rows = 64
+        k, v = synth.make_kv(rows * prompt, HEADS_KV, seed=seed, device=dev)
+        for layer in layers:
+            lk, tk, lv, tv = layer["tables"]
+            for r0 in range(0, batch, rows):
+                n = min(rows, batch - r0)
+                slots = synth.slots_for(block_table[r0:r0 + n], BS, 0, prompt)
+                write_tokens_to_paged_cache(layer["cache"], layout, block_table, slots, k[: n * prompt], v[: n * prompt],
+                                            q_points_k=lk, q_points_v=lv, thresholds_k=tk, thresholds_v=tv,
+                                            require_fast=True)
+
+    seq_lens = torch.full((batch,), prompt, dtype=torch.int32, device=dev)
+    slots = torch.zeros((batch,), dtype=torch.int32, device=dev)
+    tokens = torch.zeros((batch,), dtype=torch.int64, device=dev)
+    attn_out = torch.empty((batch, HEADS_Q, HEAD_DIM), dtype=torch.bfloat16, device=dev)
+    meta = BeyondPackedMetadata(
+        num_actual_tokens=batch, query_start_loc=torch.arange(batch + 1, dtype=torch.int32, device=dev), seq_lens=seq_lens,
+        block_table=block_table, slot_mapping=slots, max_query_len=1, max_seq_len=pages_per_seq * BS,
+        _beyond_query_start_loc_list=list(range(batch + 1)), _beyond_seq_lens_list=[pages_per_seq * BS] * batch)
+    stream = lambda: torch.cuda.current_stream(dev).cuda_stream  # noqa: E731
+    QW, KW = HEADS_Q * HEAD_DIM, HEADS_KV * HEAD_DIM
+
+    def rope(x, cos, sin):
+        x1, x2 = x[..., : HEAD_DIM // 2].float(), x[..., HEAD_DIM // 2:].float()
+        return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(torch.bfloat16)
+
+    def attention(layer, q, k, v):
+        return layer["impl"].forward(None, q, k, v, layer["cache"], meta, output=attn_out)
+
+    def model_step():
+        seq_lens.add_(1)  # the token being generated joins its context
+        _lib.call("bkv_derive_slots_sm100", seq_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+                  block_table.shape[1], BS, batch, slots.data_ptr(), stream())
+        pos = (seq_lens - 1).long()
+        cos, sin = rope_cos[pos][:, None, :], rope_sin[pos][:, None, :]
+        x = embed[tokens]
+        for layer in layers:
+            qkv = F.rms_norm(x, (HID,), layer["n1"], 1e-5) @ layer["wqkv"]
+            q = rope(qkv[:, :QW].view(batch, HEADS_Q, HEAD_DIM), cos, sin)
+            k = rope(qkv[:, QW:QW + KW].view(batch, HEADS_KV, HEAD_DIM), cos, sin)
+            v = qkv[:, QW + KW:].view(batch, HEADS_KV, HEAD_DIM)
+            x = x + attention(layer, q, k, v).view(batch, QW) @ layer["wo"]
+            gu = F.rms_norm(x, (HID,), layer["n2"], 1e-5) @ layer["wgu"]
+            x = x + (F.silu(gu[:, :FFN]) * gu[:, FFN:]) @ layer["wdown"]
+        logits = F.rms_norm(x, (HID,), final_norm, 1e-5) @ lm_head
+        tokens.copy_(logits.argmax(dim=-1))
+
+    q_fixed = torch.randn((batch, HEADS_Q, HEAD_DIM), device=dev).to(torch.bfloat16)
+    k_fixed, v_fixed = synth.make_kv(batch, HEADS_KV, seed=5, device=dev)
+
+    def attention_only_step():  # the 32 attention calls of one step on their own (share of the step)
+        for layer in layers:
+            attention(layer, q_fixed, k_fixed, v_fixed)
+
+    def reset(seed):
+        seq_lens.fill_(prompt)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed)
+        tokens.copy_(torch.randint(0, VOCAB, (batch,), generator=gen, device=dev))
+
+    fill_caches(100 + rank)
+    reset(rank)
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):  # eager passes: workspaces and library handles exist before capture
+        model_step()
+        attention_only_step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    graph, attn_graph = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        model_step()
+    with torch.cuda.graph(attn_graph):
+        attention_only_step()
+
+    def timed(g, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1)
+
+    total_ms, attn_ms = 0.0, 0.0
+    sampler = None
+    for wave in range(waves):
+        if wave:
+            fill_caches(100 + rank + 1000 * wave)
+        reset(rank + 1000 * wave)
+        for _ in range(max(3, min(args.warmup, 5))):
+            graph.replay()
+        reset(rank + 1000 * wave)
+        seq_lens.fill_(prompt + gen_steps // 2)  # attention alone at the mid-generation context length
+        attn_ms += timed(attn_graph, 5) / 5
+        reset(rank + 1000 * wave)
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        if rank == 0 and sampler is None:
+            sampler = ClockSampler(local_rank, period_s=0.02)
+        total_ms += timed(graph, gen_steps)
+    clocks = sampler.stop() if sampler is not None else None
+    finite = bool(torch.isfinite(attn_out.float()).all().item()) and int(seq_lens.max().item()) == prompt + gen_steps
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    if rank != 0:
+        return None
+    if not finite:
+        raise SystemExit("box decode: non-finite attention output or wrong final context length")
+    generated = args.box_batch * gen_steps
+    step_ms = total_ms / (waves * gen_steps)
+    return {
+        "metric": "decode_tokens_per_s_box",
+        "value": generated / (total_ms * 1e-3),
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": gen_steps,
+        "ms_per_step": step_ms,
+        "attention_ms_per_step": attn_ms / waves,
+        "attention_share": (attn_ms / waves) / step_ms,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "dtype": "bf16 weights and activations; 4-bit codes + 16-bit group statistics in the KV cache",
+        "data": "synthetic (random-init weights, uniform token ids, encode-filled contexts)",
+        "config": {"workload": f"random-init Llama-3.1-8B shape, {LAYERS} layers, {args.box_batch} requests x {prompt}-token "
+                               f"contexts + {gen_steps} generated tokens over {world} GPU(s): {batch} resident per GPU x "
+                               f"{waves} wave(s); {BS}-token pages; GEMMs / norms / activation are torch library calls, "
+                               f"attention is the packed backend"},
+        "clocks": clocks,
     }
 
 
