@@ -22,7 +22,8 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("BEYOND_REFERENCE", "/root/reference")
+# the reference checkout: $BEYOND_REFERENCE, else a directory "reference" beside this repository
+REF = os.environ.get("BEYOND_REFERENCE", os.path.join(os.path.dirname(REPO), "reference"))
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 sys.path.insert(0, REPO)

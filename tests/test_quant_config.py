@@ -200,7 +200,8 @@ def test_table_precision_contract():
 
 
 def test_matches_the_reference_loader_when_present(tmp_path):
-    ref_src = "/root/reference/src"
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref_src = os.path.join(os.environ.get("BEYOND_REFERENCE", os.path.join(os.path.dirname(repo), "reference")), "src")
     if not os.path.isdir(ref_src):
         pytest.skip("reference tree not present")
     sys.path.insert(0, ref_src)
