@@ -96,7 +96,7 @@ def test_config0_cache_checksum(golden):
 
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
 @pytest.mark.parametrize("tokens,heads,shared", [(8, 2, True), (513, 8, False), (1, 4, False), (40, 40, False),
-                                                 (20000, 8, False)])
+                                                 (20000, 8, False), (19500, 6, False), (19000, 3, False)])
 def test_writer_matches_oracle_random(tokens, heads, shared, kind):
     rng = np.random.default_rng(2708 + tokens)
     dt = KIND_TO_DTYPE[kind]
