@@ -595,6 +595,16 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
     prefill_ms = timed(lambda: encode(k, v, slots), 20)
     prefill_bytes = seqs * prompt * HEADS_KV * (512 + 160)  # bf16 K and V rows in, packed row out
 
+    # read-back of the same contexts to dense bf16 K/V (what chunked prefill attends over)
+    from beyond_kv_cache_b200.quant.beyond_cute import dequantize_paged_kv_to_dense
+    dense_k, dense_v = torch.empty_like(k), torch.empty_like(v)
+    prompt_lens = torch.full((seqs,), prompt, dtype=torch.int32, device=dev)
+    starts = torch.arange(0, (seqs + 1) * prompt, prompt, dtype=torch.int32, device=dev)
+    readback_ms = timed(lambda: dequantize_paged_kv_to_dense(cache, layout, block_table, prompt_lens, starts, dense_k,
+                                                             dense_v, max_seq_len=prompt, q_points_k=lk, q_points_v=lv,
+                                                             stat_dtype=stat_dtype), 20)
+    del dense_k, dense_v
+
     q = torch.randn((seqs, HEADS_Q, HEAD_DIM), device=dev).to(torch.bfloat16)
     out = torch.empty_like(q)
     k1, v1 = synth.make_kv(seqs, HEADS_KV, seed=99 + rank, device=dev)
@@ -628,6 +638,9 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
                            "GBps": prefill_bytes / (prefill_ms * 1e-3) / 1e9,
                            "frac_of_peak": prefill_bytes / (prefill_ms * 1e-3) / 1e9 / peak,
                            "bytes_per_token_head": 672, "peak_source": peak_kind},
+        "readback": {"ms": readback_ms, "GBps": prefill_bytes / (readback_ms * 1e-3) / 1e9,
+                     "frac_of_peak": prefill_bytes / (readback_ms * 1e-3) / 1e9 / peak,
+                     "bytes_per_token_head": 672},
         "decode_steps": {"ms_per_step": gen_ms / gen_steps, "steps": gen_steps,
                          "attended_GBps": attended / (gen_ms * 1e-3) / 1e9},
         "data": "synthetic",
