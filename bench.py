@@ -569,9 +569,10 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
     k, v = synth.make_kv(seqs * prompt, HEADS_KV, seed=7 + rank, device=dev)
     slots = synth.slots_for(block_table, BS, 0, prompt)
 
-    def encode(kk, vv, ss):
+    def encode(kk, vv, ss, signal=False):
         write_tokens_to_paged_cache(cache, layout, block_table, ss, kk, vv, q_points_k=lk, q_points_v=lv,
-                                    thresholds_k=tk, thresholds_v=tv, require_fast=True, stat_dtype=stat_dtype)
+                                    thresholds_k=tk, thresholds_v=tv, require_fast=True, stat_dtype=stat_dtype,
+                                    signal_pdl_dependents=signal)
 
     def timed(fn, reps):
         for _ in range(3):
@@ -609,7 +610,7 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
     out = torch.empty_like(q)
     k1, v1 = synth.make_kv(seqs, HEADS_KV, seed=99 + rank, device=dev)
     spec = rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=block_table, heads_q=HEADS_Q,
-                                max_seq_len=pages_per_seq * BS, num_splits=args.splits)
+                                max_seq_len=pages_per_seq * BS, num_splits=args.splits, wait_for_pdl_writer=True)
     ws = rt.allocate_runtime_workspace(spec, device=dev)
     lens = [torch.full((seqs,), prompt + i + 1, dtype=torch.int32, device=dev) for i in range(gen_steps)]
     step_slots = [synth.slots_for(block_table, BS, prompt + i, 1) for i in range(gen_steps)]
@@ -617,7 +618,7 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
 
     def generate():
         for i in range(gen_steps):
-            encode(k1, v1, step_slots[i])
+            encode(k1, v1, step_slots[i], signal=True)  # the decode grid starts its set-up behind it
             rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=block_table,
                                      seq_lens=lens[i], k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
                                      workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
@@ -684,6 +685,9 @@ def measure(args, world, rank, local_rank, dev):
     rk, rv = rt.prepare_runtime_qpoints(lk, lv, heads_kv=HEADS_KV)
     spec = rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=block_table, heads_q=HEADS_Q,
                                 max_seq_len=max_seq_len, num_splits=args.splits)
+    # the serving step runs the decode grid as a programmatic dependent of the cache writer
+    spec_pdl = rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=block_table, heads_q=HEADS_Q,
+                                    max_seq_len=max_seq_len, num_splits=args.splits, wait_for_pdl_writer=True)
     ws = rt.allocate_runtime_workspace(spec, device=dev)
     scale = synth.softmax_scale()
     streamed = (args.variant == 0 or args.variant >= 40) and "stream" in ws
@@ -755,8 +759,9 @@ def measure(args, world, rank, local_rank, dev):
     def device_part():
         d_in.copy_(h_in, non_blocking=True)
         write_tokens_to_paged_cache(cache, layout, block_table, d_slots, d_k, d_v, q_points_k=lk, q_points_v=lv,
-                                    thresholds_k=tk, thresholds_v=tv, require_fast=True, stat_dtype=stat_dtype)
-        rt.run_nonuniform_decode(spec=spec, q=d_q, cache=cache, layout=layout, block_table=block_table,
+                                    thresholds_k=tk, thresholds_v=tv, require_fast=True, stat_dtype=stat_dtype,
+                                    signal_pdl_dependents=True)
+        rt.run_nonuniform_decode(spec=spec_pdl, q=d_q, cache=cache, layout=layout, block_table=block_table,
                                  seq_lens=d_lens, k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
                                  workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
         h_out.copy_(out, non_blocking=True)

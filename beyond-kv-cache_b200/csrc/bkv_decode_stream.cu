@@ -150,7 +150,6 @@ __global__ void __maxnreg__(max_regs_for(NW))
   const bool noload = (p.flags & BKV_FLAG_DEBUG_NOLOAD) != 0;
   const bool nowait = (p.flags & BKV_FLAG_DEBUG_NOWAIT) != 0;
 
-  if (p.flags & BKV_FLAG_PDL_WAIT) pdl_wait();
   pdl_launch_dependents();  // the fix-up grid may be set up now; it waits for this grid to finish
 
   if (tid == 0) {
@@ -305,6 +304,11 @@ __global__ void __maxnreg__(max_regs_for(NW))
     if (!ok) atomicExch(&g_stream_status, 2);
     return ok;
   };
+
+  // Launched behind a cache writer that lets its dependents start early: everything above read
+  // only what older launches produced (sequence lengths); the cache is read from here on.  (In
+  // a grid that was launched the ordinary way this returns at once.)
+  if (p.flags & BKV_FLAG_PDL_WAIT) pdl_wait();
 
   for (int ph = 0; ph < 2; ++ph) {
     // ---- the part of this CTA's share that lies in its ph-th head (CTA-uniform) ------------
@@ -1240,7 +1244,29 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
     cudaFuncSetAttribute(stream_prefix_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured[p.stat_bf16 ? 1 : 0][dev] = true;
   }
-  kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp, maps.map16, maps.map4, maps.mapvs);
+  if ((sp.d.flags & BKV_FLAG_PDL_WAIT) && sp.d.batch <= kMaxBatch) {
+    // programmatic dependent launch behind the cache writer: this grid's set-up (prefix sums,
+    // shares, page ids) runs while the writer drains; it waits before its first cache read.
+    // (With the prefix sums planned by a kernel of their own that kernel is the predecessor
+    // and the set-up reads its output, so the launch stays ordinary.)
+    cudaLaunchConfig_t dcfg = {};
+    dcfg.gridDim = dim3(C);
+    dcfg.blockDim = dim3(NW * 32);
+    dcfg.dynamicSmemBytes = R::kDynBytes;
+    dcfg.stream = stream;
+    cudaLaunchAttribute dattr[1];
+    dattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    dattr[0].val.programmaticStreamSerializationAllowed = 1;
+    dcfg.attrs = dattr;
+    dcfg.numAttrs = 1;
+    const cudaError_t de = cudaLaunchKernelEx(&dcfg, kern, sp, maps.map16, maps.map4, maps.mapvs);
+    if (de != cudaSuccess) {
+      set_last_cuda_error(de, "bkv_decode_stream_sm100(decode, dependent launch)");
+      return BKV_ERR_CUDA;
+    }
+  } else {
+    kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp, maps.map16, maps.map4, maps.mapvs);
+  }
   int rc = check_launch("bkv_decode_stream_sm100(decode)");
   if (rc != BKV_OK) return rc;
   // programmatic dependent launch: the fix-up grid is set up while the decode grid drains

@@ -35,6 +35,7 @@ from ...quant.beyond_cute import (
     write_tokens_to_paged_cache,
 )
 from ...quant.fa4_cute import beyond_mixed_decode_runtime as _rt
+from .config import env_bool
 
 BEYOND_BITS = 4
 BEYOND_K_GROUP_SIZE = 32
@@ -257,9 +258,12 @@ class BeyondPackedImpl:
         batch = int(q.shape[0])
         if slots.dtype != torch.int32 or not slots.is_contiguous():
             slots = slots.to(torch.int32).contiguous()
-        # the current token is written first and then attended like any other (:2953-2969)
+        # the current token is written first and then attended like any other (:2953-2969); the
+        # writer lets the attention grid start its set-up early and that grid waits before its
+        # first cache read (BEYOND_SM103_WRITER_PDL, on by default as in the reference :2955)
+        writer_pdl = env_bool("BEYOND_SM103_WRITER_PDL", True)
         write_tokens_to_paged_cache(cache, layout, block_table, slots[:batch], k[:batch], v[:batch], q_points_k=qk,
-                                    q_points_v=qv, thresholds_k=tk, thresholds_v=tv, signal_pdl_dependents=False,
+                                    q_points_v=qv, thresholds_k=tk, thresholds_v=tv, signal_pdl_dependents=writer_pdl,
                                     require_fast=True)
         bs = int(layout.block_size)
         need = max(int(x) for x in seq_lens_cpu)
@@ -270,7 +274,8 @@ class BeyondPackedImpl:
         max_seq_len = min(bucket, capacity)
         rk, rv = self._runtime_qpoints(qk, qv)
         spec = _rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=block_table, heads_q=self.num_heads,
-                                     max_seq_len=max_seq_len, num_splits=0, qpoint_dtype=rk.dtype)
+                                     max_seq_len=max_seq_len, num_splits=0, qpoint_dtype=rk.dtype,
+                                     wait_for_pdl_writer=writer_pdl)
         ws = self._workspaces.get(spec)
         if ws is None:
             ws = _rt.allocate_runtime_workspace(spec, device=q.device)
