@@ -624,6 +624,16 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
                                      workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
 
     gen_ms = timed(generate, 5)
+    # the writer alone, one token per sequence: 50 launches per CUDA-graph replay so that the host's
+    # launch rate does not bound the figure
+    append_graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.graph(append_graph, stream=side):
+        for _ in range(50):
+            encode(k1, v1, step_slots[0])
+    torch.cuda.current_stream(dev).wait_stream(side)
+    append_ms = timed(append_graph.replay, 10) / 50
     if rank != 0:
         return None
     peak, peak_kind = measured_peak()
@@ -642,7 +652,7 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
         "readback": {"ms": readback_ms, "GBps": prefill_bytes / (readback_ms * 1e-3) / 1e9,
                      "frac_of_peak": prefill_bytes / (readback_ms * 1e-3) / 1e9 / peak,
                      "bytes_per_token_head": 672},
-        "decode_steps": {"ms_per_step": gen_ms / gen_steps, "steps": gen_steps,
+        "decode_steps": {"ms_per_step": gen_ms / gen_steps, "steps": gen_steps, "append_encode_ms": append_ms,
                          "attended_GBps": attended / (gen_ms * 1e-3) / 1e9},
         "data": "synthetic",
     }
