@@ -34,11 +34,14 @@ def test_read_request_matches_reference_bits(golden, kind):
         assert np.array_equal(bits16(got)[ok], want_bits[ok])
 
 
-@pytest.mark.parametrize("bs", [16, 64, 128])
+@pytest.mark.parametrize("bs,heads,lens", [
+    (16, 2, [137, 255, 0, 1]), (64, 2, [137, 255, 0, 1]), (128, 2, [137, 255, 0, 1]),
+    (16, 1, [33, 5]), (32, 3, [70, 0, 129]), (16, 6, [97, 64]), (16, 40, [19, 40]),
+    # more positions than warps in the grid: every warp walks several tokens, page ids read ahead
+    (16, 8, [2000, 1777, 0, 1999, 1500, 2000]),
+])
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
-def test_batched_readback_matches_oracle(bs, kind):
-    lens = [137, 255, 0, 1]
-    heads = 2
+def test_batched_readback_matches_oracle(bs, heads, lens, kind):
     lk, tk, lv, tv = tables(heads, 13)
     cache, bt = oracle_cache(lens, heads, bs, kind, 31, tk.float().numpy(), tv.float().numpy())
     dt = KIND_TO_DTYPE[kind]
