@@ -106,6 +106,14 @@ def test_writer_matches_oracle_random(tokens, heads, shared, kind):
     seed_pages = rng.integers(-(2**31), 2**31, (pages, geo.block_i32)).astype(np.int32)
     k = torch.from_numpy(rng.standard_normal((tokens, heads, 128)).astype(np.float32)).to(dt)
     v = torch.from_numpy((rng.standard_normal((tokens, heads, 128)) * 3).astype(np.float32)).to(dt)
+    if tokens >= 19000:
+        # values far below the group's range: their quotients lie under 2^-60, where the encoder's
+        # shared-divisor quotient is not redone with the IEEE division when the tables are fp16
+        k[::7, :, 5] = 2.0**-100
+        k[::11, :, 40] = -(2.0**-63)
+        k[::13, :, 41] = 2.0**-61
+        v[::5, :, 77] = 2.0**-70
+        v[::9, 0, 64:96] = torch.tensor([2.0**-90, -(2.0**-90)] * 16).to(dt)  # a whole group of tiny values
     slots = rng.permutation(pages * bs)[:tokens].astype(np.int64)
     slots[::17] = -1
     if shared:
