@@ -69,6 +69,11 @@ __device__ __forceinline__ float load_table_f32(const void* base, int idx, int d
   return dtype == BKV_BF16 ? bf16_bits_to_f32(bits) : f16_bits_to_f32(bits);
 }
 
+// an ordinary load through a shared-memory window address
+__device__ __forceinline__ float shared_f32(uint32_t addr) {
+  return *static_cast<const float*>(__cvta_shared_to_generic(addr));
+}
+
 // ---- PTX wrappers -------------------------------------------------------------
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -83,6 +83,8 @@ __global__ void __launch_bounds__(256) readback_kernel(const ReadbackParams p) {
   const int head_stride = kCompact ? kGroupsPerHead * 16 : 16 * 32;
   const float* const lvl_base = kCompact ? s_lvl + (is_v ? tables * 16 : 0) + grp * 16 : s_lvl + lane;
   void* const dst = is_v ? p.out_v : p.out_k;
+  const uint32_t lvl_a = static_cast<uint32_t>(__cvta_generic_to_shared(s_lvl));
+  const uint32_t lane4 = lane * 4;
   const uint32_t max_len = static_cast<uint32_t>(p.max_seq_len);
   const uint32_t tokens = static_cast<uint32_t>(p.batch) * max_len;  // < 2^31, checked by the launcher
   const uint32_t step = gridDim.x * warps_per_block;
@@ -137,10 +139,21 @@ __global__ void __launch_bounds__(256) readback_kernel(const ReadbackParams p) {
             word[d] = code_ptr[(head + kDepth) * code_step];
             st[d] = stat_ptr[(head + kDepth) * stat_step];
           }
-          const float* const lvl = lvl_base + head * head_stride;
           float y[8];
+          if (kCompact) {
+            const float* const lvl = lvl_base + head * head_stride;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) y[i] = __fadd_rn(__fmul_rn(lvl[((w >> (4 * i)) & 15) * kEntryStride], sc), mn);
+            for (int i = 0; i < 8; ++i) y[i] = __fadd_rn(__fmul_rn(lvl[(w >> (4 * i)) & 15], sc), mn);
+          } else {
+            // entry j of this lane's table sits at head_a + j * 128 + lane * 4: the nibble is moved
+            // to bits 7-10 and merged with the lane's bits in one logic operation
+            const uint32_t head_a = lvl_a + static_cast<uint32_t>(head) * (16 * 32 * sizeof(float));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t moved = 4 * i < 7 ? w << (7 - 4 * i) : w >> (4 * i - 7);
+              y[i] = __fadd_rn(__fmul_rn(shared_f32(head_a + ((moved & 0x780u) | lane4)), sc), mn);
+            }
+          }
           store_row8<kOut>(dst, o, y);
           o += kHeadDim;
         }
