@@ -2,26 +2,34 @@
 """Headline benchmark: packed-KV decode attention, one layer, Llama-3.1-8B shapes.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--batch B] [--ctx C] [--page P] [--splits S] [--stat fp16|bf16]
+                    [--batch B] [--ctx C] [--page P] [--splits S] [--stat fp16|bf16] [--no-extras]
 
-A *step* is one pass of the hot path over one decode batch: fused paged split-KV
-attention of one query token per request over its packed 4-bit cache (+ the
-log-sum-exp combine).  Default workload (N=1): batch 64, 32 query / 8 KV heads,
-head_dim 128, context 8192, 16-token pages, random block table, bf16 queries; the
-cache holds real codes produced by the encode-on-write kernel from N(0,1) K/V with
-four K outlier channels per head scaled by 8.
+A *step* is one pass of the hot path over one decode batch: fused paged decode attention of
+one query token per request over its packed 4-bit cache.  Default workload (N=1): batch 64,
+32 query / 8 KV heads, head_dim 128, context 8192, 16-token pages, random block table, bf16
+queries; the cache holds real codes produced by the encode-on-write kernel from N(0,1) K/V
+with four K outlier channels per head scaled by 8.
 
 ``value``  : packed-cache bytes attended per second (5 effective bits per scalar:
-             seq_len * Hkv * 160 B per request), all ranks, inputs resident in HBM.
+             seq_len * Hkv * 160 B per request), all ranks, inputs resident in HBM.  The timed
+             region is exactly ``--steps`` steps; it is repeated until at least 200 steps have
+             run and the median region is reported (``timed_regions`` says how many).
 ``e2e``    : the same metric for the full serving step through the public API with
              HOST inputs: pinned q / new-token K,V / slots / seq_lens -> device,
              encode-on-write of the new token, decode attention, output -> host.
-N > 1 (torchrun): every rank owns its own batch and page pool (request-batch
-sharding, no collective on the data path); time is the max over ranks.
+``parity`` : max-abs error of the timed output of four of the batch's requests against the
+             float64 CPU oracle over the same packed pages (checked outside the timed region).
+On one GPU the line also carries the other measurements the path is judged by (``--no-extras``
+skips them): ``sweep`` (contexts 1K / 32K / 128K at 4M KV tokens, with the bf16-KV kernels of the
+same shape), ``vs_bf16_kv`` at the default workload, ``encode`` and ``readback`` on 262 144 rows
+and the serving step of 256 sequences.  N > 1 (torchrun): every rank owns its own batch and page
+pool (request-batch sharding, no collective on the data path), time is the max over ranks, and
+``kv_split`` reports one 128K-token sequence whose KV range is split over the ranks.
 
-``--impl reference`` times the CPU implementation of the same path (numpy port of
-the reference's eager-PyTorch exact-mode attention) on the host cores, on a bounded
-sample of the same workload.
+``--impl reference`` times the reference's own CPU implementation of the same path (its
+exact-mode attention: page read-back + float32 scaled-dot-product attention per request, staged
+under ``oracle/_ref`` by ``oracle/make_ref.py``) on all host cores, on a bounded sample of the
+same workload; without the staged module it times the numpy restatement (kind "port").
 """
 
 from __future__ import annotations
@@ -53,14 +61,12 @@ def parse_args():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0, help="0 = launch policy")
     ap.add_argument("--stat", default="fp16", choices=["fp16", "bf16"])
-    ap.add_argument("--experiment-hot-pages", type=int, default=0,
-                    help="diagnostic, not a benchmark: fold the block table onto this many physical pages so "
-                         "that the packed cache is read from L2; separates DRAM effects from the rest")
-    ap.add_argument("--variant", type=int, default=0,
-                    help="0 auto (persistent tensor-core schedule), 1 CUDA-core kernel, 20+ split-grid tensor-core "
-                         "configurations, 40+ persistent configurations")
-    ap.add_argument("--cpu-sample-requests", type=int, default=0, help="0 = one per host core")
+    ap.add_argument("--loader", type=int, default=0, choices=[0, 1],
+                    help="persistent schedule: 0 = 16-byte asynchronous copies (default), 1 = tensor copies")
+    ap.add_argument("--cpu-sample-requests", type=int, default=0, help="0 = eight requests (one per core for the port)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline, e2e, parity and CPU baseline: no sweep / bf16 / encode / read-back / KV-split records")
     ap.add_argument("--dense-baseline", action="store_true",
                     help="also time bf16-KV decode attention on the same shapes: this library's plain kernel and, "
                          "when importable, flash_attn's flash_attn_with_kvcache (library code, reported as such)")
@@ -94,7 +100,7 @@ def measured_peak():
 
 def ncu_traffic_bytes(workload: str):
     """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
-    path = os.path.join(REPO, "beyond-kv-cache_b200", "ncu_traffic.json")
+    path = os.path.join(REPO, "profiles", "ncu_traffic.json")
     try:
         with open(path) as f:
             return json.load(f).get(workload)
@@ -156,7 +162,35 @@ class ClockSampler:
 
 
 def cpu_decode_baseline(args, sample_requests: int, steps: int = 1, warmup: int = 0):
-    """The oracle's decode path on the host cores (see oracle/cpu_bench.py)."""
+    """The path on the host cores: the reference's own code when it is staged under oracle/_ref
+    (kind "reference"), else the numpy restatement (kind "port")."""
+    from oracle import make_ref
+
+    stat = "f16" if args.stat == "fp16" else "bf16"
+    ref = None
+    try:
+        ref = make_ref.load_ref()
+    except Exception as exc:  # a staged module that does not import here: say so, use the port
+        print(f"bench: staged reference module failed to import ({exc!r}); timing the port", file=sys.stderr)
+    if ref is not None:
+        from oracle import ref_bench
+
+        requests = sample_requests or 8
+        secs, threads, nbytes = ref_bench.time_decode_sample(
+            ref, requests=requests, ctx=args.ctx, heads_kv=HEADS_KV, heads_q=HEADS_Q, block_size=args.page, stat=stat,
+            steps=steps, warmup=warmup)
+        out = {
+            "value": nbytes / secs / 1e9, "unit": "GB/s", "cores": threads, "kind": "reference",
+            "sample": f"{requests} of the batch's requests x ctx {args.ctx}, one decode step each through the reference's "
+                      f"own CPU path (read_request_from_paged_cache + float32 scaled_dot_product_attention per request), "
+                      f"torch with {threads} threads",
+            "seconds_per_step": secs, "same_config": False,
+        }
+        try:
+            out["quantiser"] = ref_bench.quantiser_numbers(ref)
+        except Exception as exc:
+            out["quantiser"] = {"unavailable": repr(exc)}
+        return out
     from beyond_kv_cache_b200 import synth
     from oracle.cpu_bench import time_decode_sample
 
@@ -167,23 +201,25 @@ def cpu_decode_baseline(args, sample_requests: int, steps: int = 1, warmup: int 
     requests = sample_requests or cores
     secs, workers, nbytes = time_decode_sample(
         requests=requests, ctx=args.ctx, heads_kv=HEADS_KV, heads_q=HEADS_Q, block_size=args.page, tables=tabs,
-        stat="f16" if args.stat == "fp16" else "bf16", steps=steps, warmup=warmup, workers=cores)
+        stat=stat, steps=steps, warmup=warmup, workers=cores)
     return {
         "value": nbytes / secs / 1e9,
         "unit": "GB/s",
         "cores": workers,
         "kind": "port",
         "sample": f"{requests} of the batch's requests x ctx {args.ctx}, one decode step each, numpy float64 "
-                  f"attention over the packed pages, {workers} worker processes",
-        "seconds_per_step": secs,
+                  f"attention over the packed pages, {workers} worker processes (oracle/_ref is not staged)",
+        "seconds_per_step": secs, "same_config": False,
     }
 
 
 def run_reference(args):
+    """The reference arm: rank 0 alone runs and prints; a CPU number does not grow with the GPUs,
+    so the line says n_gpus 1 whatever --gpus was."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
+    steps = max(1, min(args.steps, 5))
     warm = 1 if args.warmup > 0 else 0
     base = cpu_decode_baseline(args, args.cpu_sample_requests, steps=steps, warmup=warm)
     line = {
@@ -191,20 +227,23 @@ def run_reference(args):
         "metric": "packed_kv_decode_attention_throughput",
         "value": base["value"],
         "unit": "GB/s",
-        "n_gpus": args.gpus,
+        "n_gpus": 1,
+        "gpus_requested": args.gpus,
         "steps": steps,
         "warmup": warm,
         "ms_per_step": base["seconds_per_step"] * 1e3,
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
-        "dtype": "f64",
+        "dtype": "f32" if base["kind"] == "reference" else "f64",
         "data": "synthetic",
         "config": workload_config(args, note="bounded CPU sample: " + base["sample"]),
-        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "same_config")},
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if "quantiser" in base:
+        line["cpu_baseline"]["quantiser"] = base["quantiser"]
     print(json.dumps(line), flush=True)
 
 
@@ -275,21 +314,105 @@ def main():
         return
     if args.sweep:
         # context sweep at a constant 4M KV tokens (batch = 4M / context), one JSON line per point
-        points = [(4096, 1024), (1024, 4096), (256, 16384), (128, 32768), (64, 65536), (32, 131072)]
+        for batch, ctx in [(4096, 1024), (1024, 4096), (256, 16384), (128, 32768), (64, 65536), (32, 131072)]:
+            line = measure(sweep_point(args, batch, ctx), world, rank, local_rank, dev, light=True)
+            if rank == 0:
+                print(json.dumps(line), flush=True)
+            torch.cuda.empty_cache()
     else:
-        points = [(args.batch, args.ctx)]
-    for batch, ctx in points:
-        point = argparse.Namespace(**vars(args))
-        point.batch, point.ctx = batch, ctx
-        if args.sweep:
-            point.steps, point.no_cpu_baseline, point.dense_baseline = min(args.steps, 200), True, True
-        line = measure(point, world, rank, local_rank, dev)
+        line = measure(args, world, rank, local_rank, dev)
+        torch.cuda.empty_cache()
+        if not args.no_extras:
+            if world > 1:
+                record = guarded(lambda: kv_split_record(measure_kv_split(args, world, rank, local_rank, dev)))
+                if rank == 0:
+                    line["kv_split"] = record
+            else:
+                add_single_gpu_records(line, args, rank, local_rank, dev)
         if rank == 0:
             print(json.dumps(line), flush=True)
-        torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def guarded(fn):
+    """A side record must never cost the headline: a failure becomes its own entry."""
+    try:
+        return fn()
+    except Exception as exc:  # noqa: BLE001
+        return {"failed": repr(exc)}
+
+
+def sweep_point(args, batch, ctx):
+    point = argparse.Namespace(**vars(args))
+    point.batch, point.ctx = batch, ctx
+    point.steps, point.no_cpu_baseline, point.dense_baseline = min(args.steps, 100), True, True
+    return point
+
+
+def kv_split_record(line):
+    if line is None:
+        return None
+    return {k: line[k] for k in ("us_per_layer", "value", "unit", "n_gpus", "scaling", "parity", "exchange", "config") if k in line}
+
+
+def add_single_gpu_records(line, args, rank, local_rank, dev):
+    """The measurements next to the headline (one GPU): context sweep with the bf16-KV kernels,
+    bf16-KV at the headline workload, encode / read-back / serving step."""
+    import torch
+
+    peak, _ = measured_peak()
+
+    def bf16_ratio(rec):
+        dense = rec.get("dense_kv_baseline") or {}
+        lib = dense.get("library_flash_attn") or {}
+        out = {"packed_us": rec["us_per_layer"], "own_bf16_kernel_us": dense.get("us_per_layer"),
+               "flash_attn_bf16_us": lib.get("us_per_layer"), "flash_attn_page_tokens": lib.get("page_tokens")}
+        if lib.get("us_per_layer"):
+            out["speedup_vs_flash_attn_bf16"] = lib["us_per_layer"] / rec["us_per_layer"]
+        elif "unavailable" in lib:
+            out["flash_attn_unavailable"] = lib["unavailable"]
+        if dense.get("us_per_layer"):
+            out["speedup_vs_own_bf16_kernel"] = dense["us_per_layer"] / rec["us_per_layer"]
+        return out
+
+    def sweep():
+        points = []
+        for batch, ctx in [(4096, 1024), (128, 32768), (32, 131072)]:
+            rec = measure(sweep_point(args, batch, ctx), 1, rank, local_rank, dev, light=True)
+            torch.cuda.empty_cache()
+            points.append({"context": ctx, "batch": batch, "us": rec["us_per_layer"], "frac": rec["roofline"]["frac"],
+                           "GBps": rec["roofline"]["achieved"], "vs_bf16_kv": bf16_ratio(rec)})
+        return points
+
+    def headline_bf16():
+        point = argparse.Namespace(**vars(args))
+        point.steps, point.no_cpu_baseline, point.dense_baseline = min(args.steps, 100), True, True
+        rec = measure(point, 1, rank, local_rank, dev, light=True)
+        torch.cuda.empty_cache()
+        return bf16_ratio(rec)
+
+    def serve():
+        rec = measure_serve(args, 1, rank, local_rank, dev)
+        torch.cuda.empty_cache()
+        return rec
+
+    line["vs_bf16_kv"] = guarded(headline_bf16)
+    line["sweep"] = guarded(sweep)
+    served = guarded(serve)
+    if "failed" in served:
+        line["encode"] = line["readback"] = line["serving_step"] = served
+    else:
+        enc, rb = served["prefill_encode"], served["readback"]
+        line["encode"] = {"ms": enc["ms"], "frac": enc["frac_of_peak"], "GBps": enc["GBps"], "rows": enc["tokens"],
+                          "bytes_per_token_head": 672, "ms_in_chunks_of_8192_tokens": enc["ms_in_chunks_of_8192_tokens"],
+                          "frac_in_chunks": enc["frac_of_peak"] * enc["ms"] / enc["ms_in_chunks_of_8192_tokens"],
+                          "with_reconstruction": served["prefill_encode_reconstruct"]}
+        line["readback"] = {"ms": rb["ms"], "frac": rb["frac_of_peak"], "GBps": rb["GBps"], "rows": enc["tokens"],
+                            "bytes_per_token_head": 672}
+        line["serving_step"] = dict(served["decode_steps"], workload=served["config"]["workload"],
+                                    tokens_per_s_one_layer=served["value"])
 
 
 def measure_kv_split(args, world, rank, local_rank, dev, ctx: int = 131072):
@@ -643,7 +766,7 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
             encode(k1, v1, step_slots[i], signal=True)  # the decode grid starts its set-up behind it
             rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=block_table,
                                      seq_lens=lens[i], k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
-                                     workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
+                                     workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, loader=args.loader if spec.persistent else 0)
 
     gen_ms = timed(generate, 5)
     # the writer alone, one token per sequence: 50 launches per CUDA-graph replay so that the host's
@@ -684,9 +807,10 @@ def measure_serve(args, world, rank, local_rank, dev, seqs: int = 256, prompt: i
     }
 
 
-def measure(args, world, rank, local_rank, dev):
-    """Build the packed cache for one (batch, context) point, time the decode step and the
-    end-to-end serving step; returns the JSON line (rank 0) or None."""
+def measure(args, world, rank, local_rank, dev, light: bool = False):
+    """Build the packed cache for one (batch, context) point, time the decode step and (unless
+    `light`) the end-to-end serving step, check a sample of the output against the oracle and time
+    the CPU baseline; returns the JSON line (rank 0) or None."""
     import torch
     import torch.distributed as dist
 
@@ -726,14 +850,12 @@ def measure(args, world, rank, local_rank, dev):
                                     max_seq_len=max_seq_len, num_splits=args.splits, wait_for_pdl_writer=True)
     ws = rt.allocate_runtime_workspace(spec, device=dev)
     scale = synth.softmax_scale()
-    streamed = (args.variant == 0 or args.variant >= 40) and "stream" in ws
-
-    bt_timed = block_table % args.experiment_hot_pages if args.experiment_hot_pages > 0 else block_table
+    streamed = spec.persistent
 
     def decode_step():
-        rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=bt_timed,
+        rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=block_table,
                                  seq_lens=seq_lens, k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
-                                 workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
+                                 workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, loader=args.loader if spec.persistent else 0)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -751,18 +873,45 @@ def measure(args, world, rank, local_rank, dev):
     for _ in range(max(args.warmup, 3)):
         decode_step()
     sync_all()
+    # Exactly args.steps steps per timed region; the region is repeated until at least 200 steps have
+    # run (a region of a few milliseconds is too short for the clock sampler) and the median counts.
+    regions = 1 if light else max(1, -(-200 // max(1, args.steps)))
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for _ in range(args.steps):
-        decode_step()
-    ev1.record()
-    sync_all()
-    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    region_ms = []
+    for _ in range(regions):
+        ev0.record()
+        for _ in range(args.steps):
+            decode_step()
+        ev1.record()
+        sync_all()
+        region_ms.append(max_over_ranks(ev0.elapsed_time(ev1)))
     clocks = sampler.stop() if sampler else None
-    ms_per_step = ms_total / args.steps
+    ms_per_step = statistics.median(region_ms) / args.steps
     packed_bytes = B * ctx * HEADS_KV * BYTES_PER_TOKEN_HEAD  # per rank per step
     value = world * packed_bytes / (ms_per_step * 1e-3) / 1e9
+
+    dense = None
+    if args.dense_baseline and rank == 0:
+        dense = time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, scale, args)
+    if light:
+        if rank != 0:
+            return None
+        peak, peak_kind = measured_peak()
+        achieved = packed_bytes / (ms_per_step * 1e-3) / 1e9
+        line = {"metric": "packed_kv_decode_attention_throughput", "value": value, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "us_per_layer": ms_per_step * 1e3,
+                "config": dict(workload_config(args), schedule="persistent" if streamed else "split"),
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "peak_source": f"{peak_kind} copy bandwidth", "algorithmic_bytes_per_launch": packed_bytes},
+                "clocks": clocks}
+        if dense is not None:
+            line["dense_kv_baseline"] = dense
+        return line
+
+    # ---- the timed output against the oracle, on a sample of the batch (outside any timed region) ----
+    parity = guarded(lambda: oracle_sample_check(torch, decode_step, q, out, cache, block_table, ctx, BS, lk, lv, scale,
+                                                 args.stat)) if rank == 0 else None
 
     # ---- end-to-end serving step with host inputs --------------------------------------
     # The caller's step: fill one pinned staging buffer (q | new K row | new V row | seq_lens |
@@ -770,7 +919,7 @@ def measure(args, world, rank, local_rank, dev):
     # output, wait.  The device part is captured once into a CUDA graph through the public API
     # (the launcher neither allocates nor synchronises) and replayed per step, the way a serving
     # engine drives it; --e2e-eager issues the same calls directly.
-    e2e_steps = min(args.steps, 500)
+    e2e_steps = min(max(args.steps, 200), 500)
     nq, nkv = B * HEADS_Q * HEAD_DIM, B * HEADS_KV * HEAD_DIM
     stage_bytes = (nq + 2 * nkv) * 2 + 2 * B * 4
     h_in = torch.empty((stage_bytes,), dtype=torch.uint8).pin_memory()
@@ -799,7 +948,7 @@ def measure(args, world, rank, local_rank, dev):
                                     signal_pdl_dependents=True)
         rt.run_nonuniform_decode(spec=spec_pdl, q=d_q, cache=cache, layout=layout, block_table=block_table,
                                  seq_lens=d_lens, k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out,
-                                 workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, variant=args.variant)
+                                 workspace=ws, softmax_scale=scale, stat_dtype=stat_dtype, loader=args.loader if spec.persistent else 0)
         h_out.copy_(out, non_blocking=True)
 
     # slot of the appended token for every position the steps cycle through (the scheduler's
@@ -851,10 +1000,6 @@ def measure(args, world, rank, local_rank, dev):
     d2h = h_out.numel() * 2
     e2e_value = world * packed_bytes / (e2e_ms * 1e-3) / 1e9
 
-    dense = None
-    if args.dense_baseline and rank == 0:
-        dense = time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, spec.num_splits, scale, args)
-
     if rank == 0:
         peak, peak_kind = measured_peak()
         achieved = packed_bytes / (ms_per_step * 1e-3) / 1e9  # one GPU, one launch of the dominant kernel
@@ -865,16 +1010,17 @@ def measure(args, world, rank, local_rank, dev):
             "unit": "GB/s",
             "n_gpus": world,
             "steps": args.steps,
+            "timed_regions": regions,
             "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step,
             "us_per_layer": ms_per_step * 1e3,
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,
-            "dtype": "f16 tensor-core operands, f32 accumulate" if args.variant != 1 else "f32",
+            "dtype": "f16 tensor-core operands, f32 accumulate" if streamed else "f32",
             "data": "synthetic",
             "config": dict(workload_config(args), num_splits=0 if streamed else spec.num_splits,
-                           schedule="persistent" if streamed else "split", kernel_variant=args.variant),
+                           schedule="persistent" if streamed else "split", loader=args.loader),
             "roofline": {
                 "bound": "hbm",
                 "achieved": achieved,
@@ -884,26 +1030,63 @@ def measure(args, world, rank, local_rank, dev):
                 "peak_source": f"{peak_kind} copy bandwidth",
                 "algorithmic_bytes_per_launch": packed_bytes,
                 "traffic": ncu_traffic_bytes(workload_key),
-                "note": "duration is the whole step (decode kernel + combine kernel when split)",
+                "note": "duration is the whole step (one decode kernel; + the combine kernel under --splits)",
             },
             "e2e": {"value": e2e_value, "unit": "GB/s", "mode": e2e_mode, "ms_per_step": e2e_ms, "wall_ms_per_step": e2e_wall_ms / e2e_steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            **({"experiment": f"block table folded onto {args.experiment_hot_pages} pages (L2-resident): not a "
-                              "bandwidth measurement"} if args.experiment_hot_pages > 0 else {}),
-            "gpu_launches": args.steps * (2 if (streamed or spec.num_splits > 1) else 1),
+            "gpu_launches": args.steps * (2 if (not streamed and spec.num_splits > 1) else 1),
             "clocks": clocks,
+            "parity": parity,
         }
         if dense is not None:
             line["dense_kv_baseline"] = dense
         if world == 1 and not args.no_cpu_baseline:
             base = cpu_decode_baseline(args, args.cpu_sample_requests)
-            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample", "same_config")}
+            if "quantiser" in base:
+                line["cpu_baseline"]["quantiser"] = base["quantiser"]
         return line
     return None
 
 
-def time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, splits, scale, args):
+def oracle_sample_check(torch, decode_step, q, out, cache, block_table, ctx, BS, lk, lv, scale, stat, requests: int = 4):
+    """Run the timed step once more and compare the rows of `requests` of its requests with the
+    float64 oracle evaluated over the same packed pages (copied to the host).  The timed output is
+    16-bit, so the bound is the decode tolerance plus half a unit in the last place of the output."""
+    import numpy as np
+
+    import oracle
+
+    decode_step()
+    torch.cuda.synchronize()
+    B = int(q.shape[0])
+    picks = sorted({0, B // 3, (2 * B) // 3, B - 1})[:requests]
+    pages = (ctx + BS - 1) // BS
+    geo = oracle.PageGeometry(BS, HEADS_KV)
+    kind = "f16" if stat == "fp16" else "bf16"
+    worst, worst_rel_ulp = 0.0, 0.0
+    for b in picks:
+        ids = block_table[b, :pages].long()
+        local = cache[ids].cpu().numpy()  # this request's pages, renumbered 0 .. pages-1
+        want = oracle.decode_attention(q[b : b + 1].float().cpu().numpy(), local, geo,
+                                       np.arange(pages, dtype=np.int32)[None, :], [ctx], levels_k=lk.float().cpu().numpy(),
+                                       levels_v=lv.float().cpu().numpy(), softmax_scale=scale, stat=kind)
+        got = out[b : b + 1].float().cpu().numpy()
+        gap = np.abs(got - want)
+        worst = max(worst, float(gap.max()))
+        ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(want), 2.0**-14))) - 7)  # bf16 spacing at |want|
+        worst_rel_ulp = max(worst_rel_ulp, float((gap / ulp).max()))
+    return {"max_abs": worst, "requests": len(picks), "request_ids": picks, "output_dtype": "bf16",
+            "max_abs_in_bf16_ulps": worst_rel_ulp, "oracle": "float64 attention over the same packed pages (oracle/)",
+            "bound": "2e-3 on the un-rounded result; the timed 16-bit output adds at most half an ulp"}
+
+
+def time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, scale, args):
     """bf16-KV decode attention on the same shapes and block table (512 B per token-head)."""
+    from beyond_kv_cache_b200.quant.fa4_cute.beyond_decode_policy import modeled_splits
+
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    splits = modeled_splits(tiles=int(block_table.shape[1]), batch=B, heads_kv=HEADS_KV, sm_count=sms, page_size=BS)
     num_pages = int(block_table.max().item()) + 1
     k_pages = torch.randn((num_pages, BS, HEADS_KV, HEAD_DIM), device=dev).to(torch.bfloat16)
     v_pages = torch.randn((num_pages, BS, HEADS_KV, HEAD_DIM), device=dev).to(torch.bfloat16)
@@ -923,18 +1106,19 @@ def time_dense_baseline(torch, _lib, dev, B, ctx, BS, block_table, q, splits, sc
     for _ in range(3):
         step()
     torch.cuda.synchronize()
+    reps = max(3, min(args.steps, 20))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(reps):
         step()
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = e0.elapsed_time(e1) / reps
     nbytes = B * ctx * HEADS_KV * 512
     result = {"us_per_layer": ms * 1e3, "GBps_bf16_bytes": nbytes / (ms * 1e-3) / 1e9, "bytes_per_token_head": 512,
               "kernel": "bkv_decode_dense_sm100 (this library, CUDA cores)"}
     del k_pages, v_pages
-    result["library_flash_attn"] = time_flash_attn_library(torch, dev, B, ctx, q, scale, args.steps)
+    result["library_flash_attn"] = time_flash_attn_library(torch, dev, B, ctx, q, scale, max(3, min(args.steps, 50)))
     return result
 
 

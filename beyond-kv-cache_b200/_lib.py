@@ -32,12 +32,16 @@ SIGNATURES = {
     "bkv_encode_sm100": [_P, _P, _L, _L, _L, _L, _I, _P, _I, _L, _L, _I, _P, _L, _L, _I, _I, _I,
                          _P, _P, _P, _P, _I, _I, _I, _P, _P, _L, _L, _L, _L, _I, _P],
     "bkv_decode_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _I, _P,
-                         _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+                         _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "bkv_decode_noalloc_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _I, _P,
                                  _I, _I, _I, _I, _F, _I, _P],
     "bkv_decode_stream_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _I, _P,
-                                _P, _L, _I, _I, _I, _F, _I, _I, _P],
+                                _P, _L, _P, _I, _I, _I, _F, _I, _I, _P],
     "bkv_decode_stream_workspace_bytes": [],
+    "bkv_decode_stream_workspace_init": [_P, _L, _P],
+    "bkv_decode_tables_bytes": [_I],
+    "bkv_decode_tables_sm100": [_P, _P, _I, _I, _I, _P, _L, _P],
+    "bkv_selftest_partition": [_P, _I, _I, _I, _I],
     "bkv_selftest_division_sm100": [_c.c_uint64, _L, _I, _P, _P],
     "bkv_decode_device_status": [_P],
     "bkv_combine_sm100": [_P, _P, _P, _I, _L, _P, _I, _P, _P],
@@ -45,7 +49,7 @@ SIGNATURES = {
                                _P, _I, _I, _I, _I, _F, _I, _P],
     "bkv_combine_packed_sm100": [_P, _I, _L, _P, _I, _P, _P],
     "bkv_decode_range_stream_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _P,
-                                      _P, _P, _L, _I, _I, _I, _I, _F, _I, _I, _P],
+                                      _P, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _P],
     "bkv_readback_sm100": [_P, _L, _L, _I, _I, _I, _P, _L, _L, _P, _P, _I, _I, _P, _P, _I, _I, _I,
                            _P, _P, _I, _P],
     "bkv_decode_dense_sm100": [_P, _L, _I, _P, _P, _I, _L, _I, _I, _P, _L, _P, _P, _I, _P, _P, _P,
@@ -84,7 +88,7 @@ def load() -> ctypes.CDLL:
             fn.argtypes = argtypes
             if name in ("bkv_status_string", "bkv_last_cuda_error"):
                 fn.restype = _c.c_char_p
-            elif name == "bkv_decode_stream_workspace_bytes":
+            elif name in ("bkv_decode_stream_workspace_bytes", "bkv_decode_tables_bytes"):
                 fn.restype = _L
             else:
                 fn.restype = _I
@@ -123,3 +127,11 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 def current_stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+def stream_workspace(device: torch.device) -> torch.Tensor:
+    """Scratch of the persistent decode schedule for ``device``, prepared for its first use
+    (the request counters at its head start at zero; the kernels leave them at zero)."""
+    with torch.cuda.device(device):
+        nbytes = int(load().bkv_decode_stream_workspace_bytes())
+    return torch.zeros((nbytes,), dtype=torch.uint8, device=device)

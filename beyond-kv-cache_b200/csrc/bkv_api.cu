@@ -3,7 +3,6 @@
 
 #include <climits>
 #include <cstdio>
-#include <cstdlib>
 
 #include "bkv_decode_common.cuh"
 
@@ -21,30 +20,6 @@ int check_launch(const char* where) {
   if (e == cudaSuccess) return BKV_OK;
   set_last_cuda_error(e, where);
   return BKV_ERR_CUDA;
-}
-
-// Tuning / experiment knobs read once from the environment: BKV_MMA_CONFIG selects the
-// (warps, ring depth) instantiation of the tensor-core kernel, BKV_DEBUG_FLAGS is OR-ed
-// into the flags of every decode call.
-static int env_int(const char* name) {
-  const char* v = getenv(name);
-  return v ? atoi(v) : 0;
-}
-static int mma_config() {
-  static const int c = env_int("BKV_MMA_CONFIG");
-  return c;
-}
-// Timing experiments (skip the loads, skip the waits, force a share policy).  Most of them make
-// the kernels compute on stale data, so they are honoured only when
-// BKV_TIMING_EXPERIMENTS=1 is set as well, and say so once on stderr.
-static int debug_flags() {
-  static const int f = [] {
-    const int flags = env_int("BKV_DEBUG_FLAGS");
-    if (flags == 0 || env_int("BKV_TIMING_EXPERIMENTS") != 1) return 0;
-    fprintf(stderr, "libbkv_sm100: BKV_DEBUG_FLAGS=0x%x - timing experiment, decode results are not valid\n", flags);
-    return flags;
-  }();
-  return f;
 }
 
 static int fill_decode_params(DecodeParams& p, const void* q, int64_t q_batch_stride, int q_dtype,
@@ -66,6 +41,7 @@ static int fill_decode_params(DecodeParams& p, const void* q, int64_t q_batch_st
   if (gqa != 1 && gqa != 2 && gqa != 4 && gqa != 8) return BKV_ERR_UNSUPPORTED;
   if (page_stride_i32 < make_geom(block_size, heads_kv).block_i32) return BKV_ERR_ARG;
   if (q_batch_stride < static_cast<int64_t>(heads_q) * kHeadDim) return BKV_ERR_ARG;
+  if (!(softmax_scale > 0.f)) return BKV_ERR_ARG;  // the kernels take the maximum before scaling
   p.q = q; p.q_batch_stride = q_batch_stride; p.q_dtype = q_dtype;
   p.cache = static_cast<const uint32_t*>(cache);
   p.num_pages = num_pages; p.page_stride = page_stride_i32; p.block_size = block_size;
@@ -78,7 +54,7 @@ static int fill_decode_params(DecodeParams& p, const void* q, int64_t q_batch_st
   p.o_partial = nullptr; p.m_partial = nullptr; p.l_partial = nullptr;
   p.num_splits = 1; p.token_lo = 0; p.token_hi = INT_MAX; p.force_partial = 0;
   p.scale_log2 = softmax_scale * kLog2e;
-  p.flags = flags | debug_flags();
+  p.flags = flags;
   return BKV_OK;
 }
 
@@ -108,7 +84,7 @@ extern "C" int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dty
                                 int table_dtype, void* out, int out_dtype, float* out_f32,
                                 float* o_partial, float* m_partial, float* l_partial,
                                 int num_splits, int batch, int heads_q, int max_seq_len,
-                                float softmax_scale, int flags, int variant, bkv_stream_t stream) {
+                                float softmax_scale, int flags, bkv_stream_t stream) {
   using namespace bkv;
   DecodeParams p;
   const int rc = fill_decode_params(p, q, q_batch_stride, q_dtype, cache, num_pages,
@@ -127,9 +103,7 @@ extern "C" int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dty
   p.num_splits = num_splits;
   p.token_hi = max_seq_len;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int launched = BKV_ERR_UNSUPPORTED;
-  if (variant != 1) launched = launch_decode_mma(p, s, variant >= 20 ? variant - 20 : mma_config());
-  if (launched == BKV_ERR_UNSUPPORTED && variant <= 1) launched = launch_decode_scalar(p, s);
+  const int launched = launch_decode_scalar(p, s);
   if (launched != BKV_OK) return launched;
   if (num_splits > 1)
     return launch_combine(o_partial, m_partial, l_partial, num_splits,
@@ -139,6 +113,29 @@ extern "C" int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dty
 
 extern "C" int64_t bkv_decode_stream_workspace_bytes(void) { return bkv::stream_workspace_bytes(); }
 
+extern "C" int bkv_decode_stream_workspace_init(void* workspace, int64_t workspace_bytes, bkv_stream_t stream) {
+  return bkv::init_stream_workspace(workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t bkv_decode_tables_bytes(int heads_kv) { return heads_kv > 0 ? bkv::byte_table_bytes(heads_kv) : 0; }
+
+extern "C" int bkv_decode_tables_sm100(const void* lvl_k, const void* lvl_v, int table_dtype, int heads_kv,
+                                       int flags, void* tables, int64_t tables_bytes, bkv_stream_t stream) {
+  using namespace bkv;
+  if (!lvl_k || !lvl_v || !tables || heads_kv <= 0) return BKV_ERR_ARG;
+  if (table_dtype != BKV_F16 && table_dtype != BKV_BF16) return BKV_ERR_UNSUPPORTED;
+  if (tables_bytes < byte_table_bytes(heads_kv)) return BKV_ERR_ARG;
+  DecodeParams p = {};
+  p.lvl_k = lvl_k; p.lvl_v = lvl_v; p.table_dtype = table_dtype; p.heads_kv = heads_kv;
+  p.klevels_lane_major = (flags & BKV_FLAG_KLEVELS_LANE_MAJOR) != 0;
+  return launch_build_byte_tables(p, tables, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bkv_selftest_partition(const int32_t* tiles, int batch, int virtual_heads, int sm_count,
+                                      int max_tiles_per_request) {
+  return bkv::check_partition(tiles, batch, virtual_heads, sm_count, max_tiles_per_request);
+}
+
 extern "C" int bkv_decode_stream_sm100(const void* q, int64_t q_batch_stride, int q_dtype,
                                        const void* cache, int64_t num_pages,
                                        int64_t page_stride_i32, int block_size, int heads_kv,
@@ -146,9 +143,9 @@ extern "C" int bkv_decode_stream_sm100(const void* q, int64_t q_batch_stride, in
                                        int64_t block_table_stride, const int32_t* seq_lens,
                                        const void* lvl_k, const void* lvl_v, int table_dtype,
                                        void* out, int out_dtype, float* out_f32, void* workspace,
-                                       int64_t workspace_bytes, int batch, int heads_q,
-                                       int max_seq_len, float softmax_scale, int flags,
-                                       int variant, bkv_stream_t stream) {
+                                       int64_t workspace_bytes, const void* byte_tables, int batch,
+                                       int heads_q, int max_seq_len, float softmax_scale, int flags,
+                                       int loader, bkv_stream_t stream) {
   using namespace bkv;
   DecodeParams p;
   const int rc = fill_decode_params(p, q, q_batch_stride, q_dtype, cache, num_pages,
@@ -163,15 +160,14 @@ extern "C" int bkv_decode_stream_sm100(const void* q, int64_t q_batch_stride, in
   p.out = out; p.out_dtype = out_dtype; p.out_f32 = out_f32;
   p.num_splits = 1;
   p.token_hi = max_seq_len;
-  return launch_decode_stream(p, workspace, workspace_bytes, max_seq_len,
-                              static_cast<cudaStream_t>(stream), variant >= 40 ? variant - 40 : 0);
+  if (loader != 0 && loader != 1) return BKV_ERR_ARG;
+  return launch_decode_stream(p, workspace, workspace_bytes, byte_tables, max_seq_len,
+                              static_cast<cudaStream_t>(stream), loader);
 }
 
 extern "C" int bkv_decode_device_status(int* status_out) {
   if (!status_out) return BKV_ERR_ARG;
-  const int stream_status = bkv::read_stream_status();
-  *status_out = bkv::read_decode_status();
-  if (*status_out == 0) *status_out = stream_status;
+  *status_out = bkv::read_stream_status();
   return bkv::check_launch("bkv_decode_device_status");
 }
 
@@ -205,10 +201,10 @@ extern "C" int bkv_decode_range_stream_sm100(const void* q, int64_t q_batch_stri
                                              int64_t block_table_stride, const int32_t* seq_lens,
                                              const void* lvl_k, const void* lvl_v, int table_dtype,
                                              float* o_partial, float* m_partial, float* l_partial,
-                                             void* workspace, int64_t workspace_bytes, int batch,
-                                             int heads_q, int token_lo, int token_hi,
-                                             float softmax_scale, int flags, int variant,
-                                             bkv_stream_t stream) {
+                                             void* workspace, int64_t workspace_bytes,
+                                             const void* byte_tables, int batch, int heads_q,
+                                             int token_lo, int token_hi, float softmax_scale,
+                                             int flags, int loader, bkv_stream_t stream) {
   using namespace bkv;
   DecodeParams p;
   const int rc = fill_decode_params(p, q, q_batch_stride, q_dtype, cache, num_pages,
@@ -223,8 +219,9 @@ extern "C" int bkv_decode_range_stream_sm100(const void* q, int64_t q_batch_stri
   p.o_partial = o_partial; p.m_partial = m_partial; p.l_partial = l_partial;
   p.num_splits = 1; p.force_partial = 1;
   p.token_lo = token_lo; p.token_hi = token_hi;
-  return launch_decode_stream(p, workspace, workspace_bytes, token_hi - token_lo,
-                              static_cast<cudaStream_t>(stream), variant >= 40 ? variant - 40 : 0);
+  if (loader != 0 && loader != 1) return BKV_ERR_ARG;
+  return launch_decode_stream(p, workspace, workspace_bytes, byte_tables, token_hi - token_lo,
+                              static_cast<cudaStream_t>(stream), loader);
 }
 
 extern "C" int bkv_decode_range_sm100(const void* q, int64_t q_batch_stride, int q_dtype,
@@ -250,8 +247,5 @@ extern "C" int bkv_decode_range_sm100(const void* q, int64_t q_batch_stride, int
   p.o_partial = o_partial; p.m_partial = m_partial; p.l_partial = l_partial;
   p.num_splits = 1; p.force_partial = 1;
   p.token_lo = token_lo; p.token_hi = token_hi;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int launched = launch_decode_mma(p, s, mma_config());
-  if (launched == BKV_ERR_UNSUPPORTED) launched = launch_decode_scalar(p, s);
-  return launched;
+  return launch_decode_scalar(p, static_cast<cudaStream_t>(stream));
 }

@@ -65,13 +65,15 @@ __device__ __forceinline__ float load_v_level(const DecodeParams& p, int head, i
 }
 
 int launch_decode_scalar(const DecodeParams& p, cudaStream_t stream);
-int launch_decode_mma(const DecodeParams& p, cudaStream_t stream, int config);
-int read_decode_status();
 int launch_combine_packed(const float* records, int num_splits, int64_t rows, void* out, int out_dtype,
                           float* out_f32, cudaStream_t stream);
-int launch_decode_stream(const DecodeParams& p, void* workspace, int64_t workspace_bytes, int max_seq_len,
-                         cudaStream_t stream, int config);
+int launch_decode_stream(const DecodeParams& p, void* workspace, int64_t workspace_bytes, const void* byte_tables,
+                         int max_seq_len, cudaStream_t stream, int config);
 int64_t stream_workspace_bytes();
+int init_stream_workspace(void* workspace, int64_t workspace_bytes, cudaStream_t stream);
+int64_t byte_table_bytes(int heads_kv);
+int launch_build_byte_tables(const DecodeParams& p, void* out, cudaStream_t stream);
+int check_partition(const int* tiles, int batch, int hv, int sm_count, int max_tiles_per_request);
 int read_stream_status();
 int launch_combine(const float* o_partial, const float* m_partial, const float* l_partial,
                    int num_splits, int64_t rows, void* out, int out_dtype, float* out_f32,

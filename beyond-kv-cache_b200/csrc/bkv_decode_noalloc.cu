@@ -72,5 +72,5 @@ extern "C" int bkv_decode_noalloc_sm100(const void* q, int64_t q_batch_stride, i
                           heads_kv, stat_dtype, block_table, block_table_stride, seq_lens, lvl_k,
                           lvl_v, table_dtype, out, out_dtype, out_f32, o_partial, m_partial,
                           l_partial, num_splits, batch, heads_q, max_seq_len, softmax_scale, flags,
-                          /*variant=*/0, stream);
+                          stream);
 }

@@ -2,9 +2,10 @@
 //
 // The (kv-head, request, 16-token tile) space is one long line, head-major.  The grid is one
 // CTA per SM; CTA c owns the c-th equal share of the line and every warp of it an equal,
-// contiguous share of that.  A warp therefore streams through a run of consecutive tiles that
-// may start in the middle of one request and end in the middle of another; the byte tables are
-// built once per CTA (twice when its share straddles two heads) instead of once per split.
+// contiguous share of that (bkv_stream_partition.h).  A warp therefore streams through a run of
+// consecutive tiles that may start in the middle of one request and end in the middle of another;
+// the byte tables are set up once per CTA (twice when its share straddles two heads) instead of
+// once per split.
 //
 // A warp keeps a private ring of tiles which it fills itself with asynchronous copies (16-byte
 // cp.async pieces or tensor copies, see LOADER), running STAGES tiles ahead across request
@@ -12,30 +13,45 @@
 // When it leaves a request it either
 //   * owns the whole request: normalises and writes the attention output, or
 //   * owns a part of it:      writes an un-normalised partial (o, m, l) into one of the two
-//     slots of its range (slot 0: the request began before the range, slot 1: it goes on
-//     behind it) together with a header word naming the request.
-// The fix-up kernel walks the ranges in order, collects the chain of partials of every
-// request that was cut, and merges them by log-sum-exp.  When one request covers a CTA's whole
-// share, its warps merge in shared memory first and the CTA leaves a single partial.
+//     slots of its range and adds its tile count to the request's counter.  The warp whose
+//     addition completes the count is the last of the request: it recomputes, from the
+//     partition alone, where the other parts lie, merges them by log-sum-exp and writes the
+//     output.  Nobody waits for anybody, and no second kernel is needed.
+// When one request covers a CTA's whole share, its warps merge in shared memory first and the
+// CTA leaves a single partial (and, if it is the last, merges the chain with all its warps).
 //
-// Arithmetic and operand layouts (byte tables, group pairs) are those of bkv_decode_mma.cu with
-// three changes that remove shuffles, shared-memory traffic and padding:
+// Arithmetic: a 256-entry table indexed by a whole code BYTE returns the two fp16 levels of its
+// two nibbles as one MMA operand register, replicated so that lane l only reads bank l; the
+// per-(token, group) scale and minimum are applied outside the MMAs:
+//   s[t,h]  = c * sum_g ( scale_k[t,g] * (sum_{d in g} q[h,d] * Lk_g[code_k[t,d]]) + min_k[t,g] * sum_{d in g} q[h,d] )
+//   o[h,d]  = sum_t (p[t,h] * scale_v[t,g(d)]) * Lv_g(d)[code_v[t,d]]  +  sum_t p[t,h] * min_v[t,g(d)]
+// The queries enter the MMAs un-scaled (a bf16 or fp16 query is exact as an fp16 operand; the
+// softmax scale c is applied to the fp32 score), the probabilities are rounded to fp16 once and
+// the softmax denominator sums the rounded values, so that rounding cancels in the quotient.
+// An MMA works on one PAIR of groups {P, P+2}:
 //   * tokens sit in natural order in the QK rows (row g / g+8 = token g / g+8) and as
 //     (t, t+4) pairs in the PV k-slots; the ring slot is swizzled instead of padded;
 //   * MMA column n stands for (query head n/2, group n%2 of the pair), so a lane's two QK
 //     accumulator columns are the two groups of ONE head and its scores need no exchange;
 //   * PV row g / g+8 of MMA i hold the even / odd dimension 8*(g%4)+2i(+1) of a group, so
 //     a lane reads each V code word exactly once and uses both nibbles of every byte.
+// A tile that is processed alone (the odd last tile of a request, and every tile of a request of
+// at most four tiles) carries p*scale_v and p*min_v as an exact fp16 (high, low) pair: with a
+// handful of tokens nothing averages the rounding of that product.
 #include <math_constants.h>
 
 #include <type_traits>
 
 #include <cuda.h>
 
+#include <algorithm>
+#include <climits>
 #include <mutex>
+#include <vector>
 
 #include "bkv_decode_common.cuh"
 #include "bkv_mma_ptx.cuh"
+#include "bkv_stream_partition.h"
 
 namespace bkv {
 
@@ -64,43 +80,43 @@ static_assert(kRingLoS % 512 == 0 && kRingHi % 512 == 0 && kSlotBytes % 512 == 0
 constexpr int kLoSlotsS = (kLutAddr - kRingLoS) / kSlotBytes;
 constexpr uint32_t kPrefixAddr = kSmemEnd - 4224;  // int[kMaxBatch + 1] tiles before request b
 constexpr int kHiSlots = (kPrefixAddr - kRingHi) / kSlotBytes;
+constexpr uint32_t kBoundAddr = kRingHi + kHiSlots * kSlotBytes;  // int64[CTAs + 1]: where every CTA's share begins
+constexpr int kMaxCtas = (kPrefixAddr - kBoundAddr) / 8 - 1;
+static_assert(kMaxCtas >= 148, "the share boundaries of a full B200 grid fit behind the ring");
 constexpr uint32_t kFullBar = kSmemBase;          // 8 B each
 constexpr uint32_t kChunkTot = kSmemBase + 512;   // int[32] scan scratch
+constexpr uint32_t kPendList = kSmemBase + 640;   // int[16 warps][4]: cut requests this warp has to merge at the end
+constexpr uint32_t kPendCount = kSmemBase + 896;  // int[16 warps]
+constexpr uint32_t kPendCta = kSmemBase + 960;    // int[2]: the same for the CTA as a whole, one per phase (-1: none)
 constexpr uint32_t kLevels = kSmemBase + 1280;    // fp16 [K|V][4][16]
-constexpr int kHdrNone = -1;
-
-constexpr int BKV_FLAG_DEBUG_NOLOAD = 0x100;  // timing experiment: reuse the first ring fill
-constexpr int BKV_FLAG_DEBUG_NOWAIT = 0x200;  // timing experiment (cp.async loader): consume tiles without waiting for them
-constexpr int BKV_FLAG_DEBUG_EQUAL_SHARES = 0x800;     // experiment: force equal shares
-constexpr int BKV_FLAG_DEBUG_ALIGNED_SHARES = 0x1000;  // experiment: force head-aligned shares
+constexpr int kTableBarIndex = 63;               // the last of the 64 barrier words: byte tables landed
+constexpr int kMaxCounters = 1 << 20;            // virtual heads x batch of one launch (see launch_variant)
 
 struct StreamParams {
   DecodeParams d;
   float* ws_o;   // [slots][4][128]
   float* ws_m;   // [slots][4]  log2 domain
   float* ws_l;   // [slots][4]
-  int* ws_hdr;   // [slots]  (virtual head * batch + request) * 2 + (1: last part), or kHdrNone
+  int* ws_cnt;   // [virtual heads * batch] tiles of a cut request that have been turned into partials;
+                 // zero between launches (the warp that completes a count puts it back to zero)
   int* ws_prefix;  // [batch + 1] tiles before request b, written by stream_prefix_kernel when batch > kMaxBatch
+  const uint32_t* byte_tables;  // optional [heads_kv][2][256][64]: the two table blocks of every head, ready to copy
   int quads;     // query-head quads per kv head
   int aligned;   // 1: every CTA's share lies inside one head (heads get floor or ceil of C / heads CTAs)
   int straddle_tiles;  // equal shares: tiles by which a share that straddles two heads is shortened
   int q_vec;           // 16-bit queries whose rows can be read in 8-byte pieces
 };
 
-// one box of the packed cache, seen as [page][64-byte row][64 bytes], into a ring slot
-// the V statistics of the four groups of one head for one 16-token tile: the region is seen as
-// [page][head*4+group][tile of the page][64 bytes]
-__device__ __forceinline__ void tensor_copy_4d(uint32_t dst, const CUtensorMap* map, int tile, int row, int page,
+// Tensor copies of the packed cache.  A page is two halves of the same shape - K codes + K
+// statistics | V codes + V statistics - so the cache is described as uint8
+// [page][half][64-byte row][64]: one copy with a box of two halves brings the K and the V
+// rows of a tile in together.  The V statistics of pages longer than one tile are group-major
+// and get a view of their own: [page][head*4+group][tile of the page][64].
+__device__ __forceinline__ void tensor_copy_4d(uint32_t dst, const CUtensorMap* map, int c1, int c2, int c3,
                                                uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
-      "l"(map), "r"(0), "r"(tile), "r"(row), "r"(page), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tensor_copy_3d(uint32_t dst, const CUtensorMap* map, int row, int page, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-      "l"(map), "r"(0), "r"(row), "r"(page), "r"(bar)
+      "l"(map), "r"(0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
 }
 
@@ -116,14 +132,169 @@ struct Ring {
   }
 };
 
+// 16 consecutive floats of a result row, rounded to the output type
+__device__ __forceinline__ void store_out16(void* out, int64_t idx, int dtype, const float (&v)[16]) {
+  if (dtype == BKV_F32) {
+    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + idx);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    return;
+  }
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t lo2 = dtype == BKV_BF16 ? f32_to_bf16_bits(v[2 * i]) : f32_to_f16_bits(v[2 * i]);
+    const uint32_t hi2 = dtype == BKV_BF16 ? f32_to_bf16_bits(v[2 * i + 1]) : f32_to_f16_bits(v[2 * i + 1]);
+    w[i] = lo2 | (hi2 << 16);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned short*>(out) + idx);
+  dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// Where the merged result of a cut request goes.  Everything is passed BY VALUE to the
+// (deliberately not inlined) merge routine: handing it a reference to the kernel's parameter
+// block would force that block into local memory for the whole kernel.
+struct MergeIo {
+  const int64_t* bounds;  // shared memory: tile at which the share of CTA c begins, c = 0 .. CTAs
+  const float* ws_o;  // partial slots [slot][4][128], [slot][4], [slot][4]
+  const float* ws_m;
+  const float* ws_l;
+  float* stage;       // not null: the caller's [4][128 | m | l] staging record in shared memory (CTA-level merge)
+  void* out;          // else: final result rows ...
+  float* out_f32;
+  float* o_partial;   // ... or, with force_partial, un-normalised rows for a merge across ranks
+  float* m_partial;
+  float* l_partial;
+  int out_dtype;
+  int force_partial;
+  int64_t row0;       // result row of query head 0 of the quad
+  int nh;             // live query heads of the quad
+};
+
+// Log-sum-exp merge of parts of the cut request whose tiles are [pb, pe) of virtual head vh.
+// Where the parts lie follows from the partition alone (bkv_stream_partition.h): lane i of the
+// warp works out what CTA c0+i leaves, a scan numbers the parts, and the warp then loads them
+// six at a time.  The calling warp takes the batches begin, begin+step, ...; lane l accumulates
+// query head l>>3 of the quad, dimensions 16*(l&7) .. +15.  The partials were written by other
+// SMs, so they are read from L2.
+__device__ __noinline__ void merge_parts(const MergeIo io, const part::Plan pl, const int vh, const int pb, const int pe,
+                                         const int begin, const int step) {
+  constexpr uint32_t kAll = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  const int h = lane >> 3, dc = lane & 7;
+  float M = -CUDART_INF_F, den = 0.f, num[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) num[i] = 0.f;
+  constexpr int kBatch = 6;  // parts loaded at once (one L2 round trip)
+  int batch = 0;
+  const int64_t g0 = static_cast<int64_t>(vh) * pl.Tb + pb, g1 = static_cast<int64_t>(vh) * pl.Tb + pe;
+  for (int c0 = 0; c0 < pl.C; c0 += 32) {
+    // which of these 32 CTAs hold tiles of the request at all: two loads and two compares per lane
+    int64_t ga = 0, gb = 0;
+    if (c0 + lane < pl.C) {
+      ga = io.bounds[c0 + lane];
+      gb = io.bounds[c0 + lane + 1];
+    }
+    const bool meets = ga < g1 && gb > g0;
+    if (!__any_sync(kAll, meets)) continue;
+    part::CtaParts cp = {0u, 0, 0, 0};
+    if (meets) cp = part::cta_parts(pl, ga, gb, vh, pb, pe);
+    const int cnt = __popc(cp.mask);
+    int incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(kAll, incl, o);
+      if (lane >= o) incl += y;
+    }
+    const int total = __shfl_sync(kAll, incl, 31);
+    const int pre = incl - cnt;  // parts of this round before those of this lane's CTA
+    const uint32_t info = cp.mask | (static_cast<uint32_t>(cp.ph) << 16) | (static_cast<uint32_t>(cp.solo) << 17) |
+                          (static_cast<uint32_t>(cp.starts) << 18);
+    for (int j0 = 0; j0 < total; j0 += kBatch, ++batch) {
+      if (batch < begin || (batch - begin) % step != 0) continue;
+      float o2[kBatch][16], m2[kBatch], l2[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int j = j0 + u;
+        m2[u] = 0.f;
+        l2[u] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o2[u][i] = 0.f;
+        if (j < total) {  // uniform over the warp
+          const int owner = 31 - __clz(__ballot_sync(kAll, pre <= j));  // pre is non-decreasing over the lanes
+          const uint32_t oi = __shfl_sync(kAll, info, owner);
+          const int nth = j - __shfl_sync(kAll, pre, owner);  // which of the owner's parts
+          uint32_t mk = oi & 0xFFFFu;
+          for (int i = 0; i < nth; ++i) mk &= mk - 1;
+          const int w = __ffs(mk) - 1;
+          const bool solo = (oi >> 17) & 1u;
+          const int starts = ((oi >> 18) & 1u) && nth == 0;
+          const int64_t row = static_cast<int64_t>(part::part_slot(pl, c0 + owner, (oi >> 16) & 1, solo ? 0 : w, starts)) * 4 + h;
+          m2[u] = __ldcg(io.ws_m + row);
+          l2[u] = __ldcg(io.ws_l + row);
+          const float4* src = reinterpret_cast<const float4*>(io.ws_o + row * kHeadDim + dc * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 v = __ldcg(src + i);
+            o2[u][4 * i] = v.x;
+            o2[u][4 * i + 1] = v.y;
+            o2[u][4 * i + 2] = v.z;
+            o2[u][4 * i + 3] = v.w;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        if (!(l2[u] > 0.f)) continue;
+        const float Mn = fmaxf(M, m2[u]);
+        const float a = (M == -CUDART_INF_F) ? 0.f : exp2f(M - Mn);
+        const float wgt = exp2f(m2[u] - Mn);
+        den = den * a + l2[u] * wgt;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) num[i] = num[i] * a + o2[u][i] * wgt;
+        M = Mn;
+      }
+    }
+  }
+  if (io.stage) {  // one warp's share of a CTA-level merge: the CTA folds the warps' records
+    float4* dst = reinterpret_cast<float4*>(io.stage + h * kHeadDim + dc * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = make_float4(num[4 * i], num[4 * i + 1], num[4 * i + 2], num[4 * i + 3]);
+    if (dc == 0) {
+      io.stage[4 * kHeadDim + h] = M;
+      io.stage[4 * kHeadDim + 4 + h] = den;
+    }
+    return;
+  }
+  if (h >= io.nh) return;
+  const int64_t row = io.row0 + h;
+  if (io.force_partial) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) io.o_partial[row * kHeadDim + dc * 16 + i] = den > 0.f ? num[i] : 0.f;
+    if (dc == 0) {
+      io.m_partial[row] = den > 0.f ? M * kLn2 : -CUDART_INF_F;
+      io.l_partial[row] = den;
+    }
+    return;
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) num[i] *= inv;
+  store_out16(io.out, row * kHeadDim + dc * 16, io.out_dtype, num);
+  if (io.out_f32) store_out16(io.out_f32, row * kHeadDim + dc * 16, BKV_F32, num);
+}
+
 // LOADER 1: every lane moves 16-byte pieces with cp.async, one commit group per tile.
-// LOADER 3: an elected lane issues one tensor copy (cp.async.bulk.tensor) per part of a tile,
-// completing on one mbarrier per ring stage; the copies bypass the load/store pipe.
+// LOADER 3: an elected lane issues two (16-token pages) or three tensor copies
+// (cp.async.bulk.tensor) per tile, completing on one mbarrier per ring stage; the copies bypass
+// the load/store pipe.
 template <int NW, int STAGES, bool STAT_BF16, int LOADER, int PAIR = 2>
 __global__ void __maxnreg__(max_regs_for(NW))
-    decode_stream_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap map16,
-                         const __grid_constant__ CUtensorMap map4, const __grid_constant__ CUtensorMap mapvs) {
+    decode_stream_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap map_code,
+                         const __grid_constant__ CUtensorMap map_stat, const __grid_constant__ CUtensorMap map_vstat) {
   static_assert(STAGES <= 4, "cp_async_wait_pending handles up to three groups in flight");
+  static_assert(NW * STAGES < kTableBarIndex, "the last barrier word belongs to the byte tables");
   using R = Ring<NW, STAGES>;
   const DecodeParams& p = sp.d;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -147,15 +318,15 @@ __global__ void __maxnreg__(max_regs_for(NW))
   const int tiles_per_page = 1 << log2r;
   const int lo = max(p.token_lo, 0);
   const int page_lo = lo / BS;
-  const bool noload = (p.flags & BKV_FLAG_DEBUG_NOLOAD) != 0;
-  const bool nowait = (p.flags & BKV_FLAG_DEBUG_NOWAIT) != 0;
-
-  pdl_launch_dependents();  // the fix-up grid may be set up now; it waits for this grid to finish
 
   if (tid == 0) {
     for (int i = 0; i < NW * STAGES; ++i) mbar_init(kFullBar + 8 * i, 1);
+    mbar_init(kFullBar + 8 * kTableBarIndex, 1);
     fence_barrier_init();
+    reinterpret_cast<int*>(gptr(kPendCta))[0] = -1;
+    reinterpret_cast<int*>(gptr(kPendCta))[1] = -1;
   }
+  if (tid < 16) reinterpret_cast<int*>(gptr(kPendCount))[tid] = 0;
 
   // ---- tiles before every request (exclusive prefix sum over the batch) ------------------
   const bool planned = B > kMaxBatch;
@@ -213,47 +384,44 @@ __global__ void __maxnreg__(max_regs_for(NW))
       }
     }
   }
-  const int64_t G = static_cast<int64_t>(p.heads_kv * quads) * Tb;
-  int64_t ga, gb;  // this CTA's share of the line
-  if (sp.aligned) {
-    // heads 0..extra-1 are served by base+1 CTAs, the others by base; no share straddles two
-    // heads, so the tables are built once, at the price of unequal shares
-    const int hv = p.heads_kv * quads;
-    const int base = C / hv, extra = C - base * hv;
-    int h, idx, cnt;
-    if (cta < extra * (base + 1)) {
-      h = cta / (base + 1);
-      idx = cta - h * (base + 1);
-      cnt = base + 1;
-    } else {
-      const int c2 = cta - extra * (base + 1);
-      h = extra + c2 / base;
-      idx = c2 - (c2 / base) * base;
-      cnt = base;
-    }
-    ga = static_cast<int64_t>(h) * Tb + static_cast<int64_t>(Tb) * idx / cnt;
-    gb = static_cast<int64_t>(h) * Tb + static_cast<int64_t>(Tb) * (idx + 1) / cnt;
-  } else {
-    // Equal shares of COST: a CTA whose share straddles two heads builds the tables twice and
-    // restarts its pipelines, which is worth `straddle_tiles` tiles.  The cost line is the tile
-    // line with a gap of that length at every head boundary; a share that contains a gap is
-    // that much shorter in tiles, one that ends inside a gap ends at the head boundary.
-    const int hv = p.heads_kv * quads;
-    const int64_t gap = sp.straddle_tiles;
-    const int64_t L = G + (hv - 1) * gap;
-    auto to_tile = [&](int64_t x) {
-      int64_t shift = 0;
-      for (int h = 1; h < hv; ++h) {
-        const int64_t start = static_cast<int64_t>(h) * Tb + (h - 1) * gap;
-        if (x >= start + gap) shift += gap;
-        else if (x > start) return static_cast<int64_t>(h) * Tb;
-        else break;
-      }
-      return x - shift;
-    };
-    ga = to_tile(L * cta / C);
-    gb = to_tile(L * (cta + 1) / C);
+  // (rebuilt where it is needed: nothing of it has to stay in registers through the tile loop)
+  auto make_plan = [&] {
+    part::Plan pl;
+    pl.C = gridDim.x;
+    pl.NW = NW;
+    pl.hv = p.heads_kv * sp.quads;
+    pl.Tb = prefix[p.batch];
+    pl.aligned = sp.aligned;
+    pl.gap = sp.straddle_tiles;
+    return pl;
+  };
+  int64_t* const bounds = reinterpret_cast<int64_t*>(gptr(kBoundAddr));
+  auto make_io = [&](float* stage, int64_t row0, int nh) {
+    MergeIo io;
+    io.bounds = bounds;
+    io.ws_o = sp.ws_o;
+    io.ws_m = sp.ws_m;
+    io.ws_l = sp.ws_l;
+    io.stage = stage;
+    io.out = p.out;
+    io.out_f32 = p.out_f32;
+    io.o_partial = p.o_partial;
+    io.m_partial = p.m_partial;
+    io.l_partial = p.l_partial;
+    io.out_dtype = p.out_dtype;
+    io.force_partial = p.force_partial;
+    io.row0 = row0;
+    io.nh = nh;
+    return io;
+  };
+  // where every CTA's share of the line begins (the merges at the end look the shares up here)
+  for (int c = tid; c <= C; c += NW * 32) {
+    int64_t a, e;
+    part::share_of(make_plan(), min(c, C - 1), &a, &e);
+    bounds[c] = c < C ? a : e;
   }
+  __syncthreads();
+  const int64_t ga = bounds[cta], gb = bounds[cta + 1];  // this CTA's share
 
   // ---- per-lane roles (see the file comment) ----------------------------------------------
   const int ksel = tig >> 1, khalf = tig & 1;     // QK: this lane's k-slots carry half khalf of group 2*ksel+P
@@ -287,6 +455,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
   int n_issued = 0, n_done = 0;
   uint32_t bad_mask = 0;  // bit s: the tile now in stage s maps to no page
   bool dead = false;      // a bounded wait gave up: stop working, keep walking to the barriers
+  uint32_t table_parity = 0;
 
   const PageGeom geo = make_geom(BS, p.heads_kv);
   const int64_t page_bytes = p.page_stride * 4;
@@ -312,33 +481,22 @@ __global__ void __maxnreg__(max_regs_for(NW))
 
   for (int ph = 0; ph < 2; ++ph) {
     // ---- the part of this CTA's share that lies in its ph-th head (CTA-uniform) ------------
-    int vh = 0, span = 0, first = 0;
-    if (Tb > 0 && gb > ga) {
-      vh = static_cast<int>(ga / Tb) + ph;
-      const int64_t h0 = static_cast<int64_t>(vh) * Tb;
-      const int64_t a = max(ga, h0), e = min(gb, h0 + Tb);
-      span = e > a ? static_cast<int>(e - a) : 0;
-      first = static_cast<int>(a - h0);
-    }
+    const part::Span sh = part::phase_span(make_plan(), ga, gb, ph);
+    const int vh = sh.vh, span = sh.span, first = sh.first;
     const int range = (cta * 2 + ph) * NW + warp;
-    if (lane == 0) {
-      sp.ws_hdr[2 * range] = kHdrNone;
-      sp.ws_hdr[2 * range + 1] = kHdrNone;
-    }
     if (span == 0) continue;
     const int head = vh / quads, quad = vh - head * quads;
     const int hq0 = head * gqa + quad * 4;
     const int nh = min(4, gqa - quad * 4);
 
     // ---- this warp's run of tiles [wa, wb) inside the head ---------------------------------
-    const int wa = first + static_cast<int>(static_cast<int64_t>(span) * warp / NW);
-    const int wb = first + static_cast<int>(static_cast<int64_t>(span) * (warp + 1) / NW);
+    const int wa = part::run_begin(sh, NW, warp), wb = part::run_begin(sh, NW, warp + 1);
     const int total = wb - wa;
     const bool work = total > 0 && !dead;
     // this head's level tables: requested now, stored to shared memory after the first ring fill
     // has been issued, so the read overlaps the page-id read below
     float level_early = 0.f;
-    if (tid < 128) {
+    if (tid < 128 && !sp.byte_tables) {
       const int which = tid >> 6, g = (tid >> 4) & 3, c = tid & 15;
       level_early = which ? load_v_level(p, head, g, c) : load_k_level(p, head, g, c);
     }
@@ -360,10 +518,9 @@ __global__ void __maxnreg__(max_regs_for(NW))
       ld_stat_dst = swz(kSwVStat + g * 64 + c * 16);
       ld_stat_sub = 64;
     }
-    // tensor-copy loader: 64-byte rows of the four parts inside a page
-    const int row_kcode = (geo.k_code_off * 4 + code_head) >> 6;
-    const int row_kstat = ((geo.k_stat_off + head * (BS * 4)) * 4) >> 6;
-    const int row_vcode = (geo.v_code_off * 4 + code_head) >> 6;
+    // tensor-copy loader: 64-byte rows of the code and the statistic part inside each half of a page
+    const int row_code = code_head >> 6;
+    const int row_stat = ((geo.k_stat_off + head * (BS * 4)) * 4) >> 6;
 
     // request that holds tile x of the head (prefix[b] <= x < prefix[b+1])
     auto request_of = [&](int x) {
@@ -418,15 +575,19 @@ __global__ void __maxnreg__(max_regs_for(NW))
         const uint32_t bar = bar_base + 8 * stage;
         if (elect_one_sync()) {
           mbar_arrive_expect_tx(bar, kSlotBytes);
-          tensor_copy_3d(dst + kSwKCode, &map16, row_kcode + sub * 16, phys, bar);
-          tensor_copy_3d(dst + kSwVCode, &map16, row_vcode + sub * 16, phys, bar);
-          tensor_copy_3d(dst + kSwKStat, &map4, row_kstat + sub * 4, phys, bar);
-          tensor_copy_4d(dst + kSwVStat, &mapvs, sub, head * 4, phys, bar);
+          // K and V codes in one copy: rows row_code.. of both halves of the page
+          tensor_copy_4d(dst + kSwKCode, &map_code, row_code + sub * 16, 0, phys, bar);
+          if (tiles_per_page == 1) {  // the statistics of both halves likewise
+            tensor_copy_4d(dst + kSwKStat, &map_stat, row_stat, 0, phys, bar);
+          } else {
+            tensor_copy_4d(dst + kSwKStat, &map_stat, row_stat + sub * 4, 0, phys, bar);
+            tensor_copy_4d(dst + kSwVStat, &map_vstat, sub, head * 4, phys, bar);
+          }
         }
       }
       ++n_issued;
     };
-    if (work && (!noload || n_issued == 0)) {  // first ring fill: in flight while the tables are built
+    if (work) {  // first ring fill: in flight while the tables are set up
       int st = s;
       for (int j = 0; j < min(total, STAGES); ++j) {
         issue(j, st);
@@ -435,9 +596,22 @@ __global__ void __maxnreg__(max_regs_for(NW))
     }
 
     __syncthreads();  // the previous head's tables are no longer read
-    if (tid < 128) reinterpret_cast<__half*>(gptr(kLevels))[tid] = __float2half_rn(level_early);  // fp16 [K|V][4][16]
-    __syncthreads();
-    {  // byte -> (level[low nibble], level[high nibble]) tables, one copy per bank.
+    if (sp.byte_tables) {
+      // the two table blocks of this head were laid out once per layer: two bulk copies
+      const uint32_t bar = kFullBar + 8 * kTableBarIndex;
+      if (tid == 0) {
+        fence_proxy_async();  // the reads of the old tables before the writes of the copy unit
+        mbar_arrive_expect_tx(bar, 2 * kLutBlock);
+        const char* const src = reinterpret_cast<const char*>(sp.byte_tables) + static_cast<int64_t>(head) * (2 * kLutBlock);
+        bulk_copy_g2s(kLutAddr, src, kLutBlock, bar);
+        bulk_copy_g2s(kLutAddr + kLutBlock, src + kLutBlock, kLutBlock, bar);
+      }
+      if (!wait_full(bar, table_parity)) dead = true;
+      table_parity ^= 1u;
+    } else {
+      if (tid < 128) reinterpret_cast<__half*>(gptr(kLevels))[tid] = __float2half_rn(level_early);  // fp16 [K|V][4][16]
+      __syncthreads();
+      // byte -> (level[low nibble], level[high nibble]) tables, one copy per bank.
        // Block P (P = 0, 1) holds, in bank l, the K table of group 2*((l>>1)&1)+P and the
        // V table of group 2*(l>>4)+P: the groups lane l needs when an MMA works on pair P.
       const unsigned short* lv = reinterpret_cast<const unsigned short*>(gptr(kLevels));
@@ -451,8 +625,8 @@ __global__ void __maxnreg__(max_regs_for(NW))
         row[lane] = kval;
         row[32 + lane] = vval;
       }
+      __syncthreads();
     }
-    __syncthreads();
 
     // One request covers this CTA's whole share (few, long requests): the warps do not leave a
     // partial each; they merge in shared memory and the CTA leaves one, so a request's chain of
@@ -461,8 +635,8 @@ __global__ void __maxnreg__(max_regs_for(NW))
     const bool solo = prefix[solo_b + 1] >= first + span;
 
     // ---- attention state of the request being streamed ------------------------------------
-    uint32_t qb[2][4][2];  // B operand of QK: q of head hcol, pre-scaled by softmax_scale * log2(e)
-    float qs[4];           // sum over the dims of group g of the rounded q of head tig
+    uint32_t qb[2][4][2];  // B operand of QK: q of head hcol as fp16 (exact for 16-bit queries)
+    float qs[4];           // sum over the dims of group g of the fp16 q of head tig
     float oacc[2][4][4], cmin[2][4];
     float m_used = -CUDART_INF_F, l_run = 0.f;  // head tig
 
@@ -473,6 +647,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
                        const int nvB, auto&& before_second, auto&& after_reads) {
       constexpr int NT = decltype(nt_tag)::value;
       constexpr bool PARTIAL = decltype(partial_tag)::value;
+      constexpr bool PRECISE = NT == 1;  // p*scale_v and p*min_v as exact (high, low) fp16 pairs
       const uint32_t sb[2] = {sbA, sbB};
       const int nv[2] = {nvA, nvB};
       // ------------------------------ S = Lk * Qblock (one accumulator per tile and pair) ----
@@ -542,11 +717,13 @@ __global__ void __maxnreg__(max_regs_for(NW))
         }
       }
       // ------------------------------ online softmax over the tile(s) -------------------------
+      // (the scores are still un-scaled; the scale is positive, so the maximum commutes with it)
       float tmax = fmaxf(sc[0][0], sc[0][1]);
       if (NT == 2) tmax = fmaxf(tmax, fmaxf(sc[NT - 1][0], sc[NT - 1][1]));
       tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 4));
       tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 8));
       tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 16));
+      tmax *= p.scale_log2;
       const bool need = tmax > m_used + kRescaleThreshold;
       if (__any_sync(kFull, need)) {
         const float m_new = need ? tmax : m_used;
@@ -566,9 +743,11 @@ __global__ void __maxnreg__(max_regs_for(NW))
       uint32_t ph2[NT][2];  // [tile][k-slots 2tig.. / 2tig+8..]: probabilities of head hcol, two tokens each
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const float e0 = fast_exp2(sc[t][0] - m_used), e1 = fast_exp2(sc[t][1] - m_used);
-        l_run += e0 + e1;
+        const float e0 = fast_exp2(fmaf(sc[t][0], p.scale_log2, -m_used)), e1 = fast_exp2(fmaf(sc[t][1], p.scale_log2, -m_used));
         const uint32_t mine = pack_half2(e0, e1);  // head tig: (token gid, token gid+8)
+        // the denominator sums what the PV product will use: the rounding of p cancels in o / l
+        const float2 er = __half22float2(*reinterpret_cast<const __half2*>(&mine));
+        l_run += er.x + er.y;
         const uint32_t fromA = __shfl_sync(kFull, mine, src_lane0);  // tokens of k-slots 2tig, 2tig+8
         const uint32_t fromB = __shfl_sync(kFull, mine, src_lane1);  // tokens of k-slots 2tig+1, 2tig+9
         ph2[t][0] = __byte_perm(fromA, fromB, 0x5410);
@@ -579,6 +758,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
       for (int t = 0; t < NT; ++t) {
         const uint32_t sa0 = sb[t] + vs_off0, sa1 = sb[t] + vs_off1;
         uint32_t wb2[2][2], mb2[2][2];  // [pair][k-slots 2tig.. / 2tig+8..]
+        uint32_t wl2[2][2], ml2[2][2];  // PRECISE: what the fp16 rounding of the two products dropped
 #pragma unroll
         for (int P = 0; P < 2; ++P) {
 #pragma unroll
@@ -597,13 +777,22 @@ __global__ void __maxnreg__(max_regs_for(NW))
               mn2 = __byte_perm(fst, snd, 0x7632);
             }
             uint32_t wv = hmul2_u32(ph2[t][o], sc2), mv = hmul2_u32(ph2[t][o], mn2);
+            uint32_t wl = 0u, ml = 0u;
+            if (PRECISE) {  // p*s - round(p*s) is exact in fp16 (a fused multiply-add rounds once)
+              wl = hfma2_u32(ph2[t][o], sc2, wv ^ 0x80008000u);
+              ml = hfma2_u32(ph2[t][o], mn2, mv ^ 0x80008000u);
+            }
             if (PARTIAL) {  // 0 * NaN would poison the accumulators
               const uint32_t keep = (tig + 8 * o < nv[t] ? 0x0000FFFFu : 0u) | (tig + 4 + 8 * o < nv[t] ? 0xFFFF0000u : 0u);
               wv &= keep;
               mv &= keep;
+              wl &= keep;
+              ml &= keep;
             }
             wb2[P][o] = wv;
             mb2[P][o] = mv;
+            wl2[P][o] = wl;
+            ml2[P][o] = ml;
           }
         }
         after_reads(t);  // nothing of this tile is read from the ring any more
@@ -623,6 +812,11 @@ __global__ void __maxnreg__(max_regs_for(NW))
           for (int i = 0; i < 4; ++i) mma16816(oacc[P][i], av[i][0], av[i][1], av[i][2], av[i][3], wb2[P][0], wb2[P][1]);
           const uint32_t ones = 0x3C003C00u;
           mma16816(cmin[P], ones, ones, ones, ones, mb2[P][0], mb2[P][1]);
+          if (PRECISE) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mma16816(oacc[P][i], av[i][0], av[i][1], av[i][2], av[i][3], wl2[P][0], wl2[P][1]);
+            mma16816(cmin[P], ones, ones, ones, ones, ml2[P][0], ml2[P][1]);
+          }
         }
       }
     };
@@ -640,7 +834,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
       {  // query fragments and group sums of request b
         const bool live_h = hcol < nh;
         const int64_t qoff = static_cast<int64_t>(b) * p.q_batch_stride + static_cast<int64_t>(hq0 + hcol) * kHeadDim;
-        float part[2] = {0.f, 0.f};
+        float qsum[2] = {0.f, 0.f};
 #pragma unroll
         for (int P = 0; P < 2; ++P)
 #pragma unroll
@@ -654,24 +848,24 @@ __global__ void __maxnreg__(max_regs_for(NW))
               for (int i = 0; i < 4; ++i) {
                 const uint32_t bits = (i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xFFFFu);
                 const float v = p.q_dtype == BKV_BF16 ? bf16_bits_to_f32(bits) : f16_bits_to_f32(bits);
-                f[i] = live_h ? v * p.scale_log2 : 0.f;
+                f[i] = live_h ? v : 0.f;
               }
             } else {
 #pragma unroll
-              for (int i = 0; i < 4; ++i) f[i] = live_h ? load_q(p.q, qoff + d0 + i, p.q_dtype) * p.scale_log2 : 0.f;
+              for (int i = 0; i < 4; ++i) f[i] = live_h ? load_q(p.q, qoff + d0 + i, p.q_dtype) : 0.f;
             }
             const uint32_t lo2 = pack_half2(f[0], f[1]), hi2 = pack_half2(f[2], f[3]);
             const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo2));
             const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&hi2));
-            part[P] += (a.x + a.y) + (c.x + c.y);
+            qsum[P] += (a.x + a.y) + (c.x + c.y);
             qb[P][j][0] = ksel == gsel ? lo2 : 0u;  // the other group of the pair meets zeros
             qb[P][j][1] = ksel == gsel ? hi2 : 0u;
           }
 #pragma unroll
         for (int P = 0; P < 2; ++P) {
-          part[P] += __shfl_xor_sync(kFull, part[P], 1);  // both halves of the group
+          qsum[P] += __shfl_xor_sync(kFull, qsum[P], 1);  // both halves of the group
 #pragma unroll
-          for (int e = 0; e < 2; ++e) qs[2 * e + P] = __shfl_sync(kFull, part[P], (2 * tig) * 4 + 2 * e);
+          for (int e = 0; e < 2; ++e) qs[2 * e + P] = __shfl_sync(kFull, qsum[P], (2 * tig) * 4 + 2 * e);
         }
       }
 #pragma unroll
@@ -686,15 +880,20 @@ __global__ void __maxnreg__(max_regs_for(NW))
       m_used = -CUDART_INF_F;
       l_run = 0.f;
 
+      if (x + (kend - k0) < wb && b + 1 < B) {  // the next request's queries: on their way to L2 meanwhile
+        const int esize = p.q_dtype == BKV_F32 ? 4 : 2;
+        const char* const nq = reinterpret_cast<const char*>(p.q) +
+                               (static_cast<int64_t>(b + 1) * p.q_batch_stride + static_cast<int64_t>(hq0) * kHeadDim) * esize;
+        if (lane * 128 < nh * kHeadDim * esize) asm volatile("prefetch.global.L2 [%0];" ::"l"(nq + lane * 128));
+      }
       for (int k = k0; k < kend;) {
-        const int cnt = min(PAIR, kend - k);
+        // a request of a few tiles is processed one tile at a time, i.e. by the precise form
+        const int cnt = nb <= 4 ? 1 : min(PAIR, kend - k);
         const int sB = s + 1 == STAGES ? 0 : s + 1;
         const uint32_t phaseB = s + 1 == STAGES ? phase ^ 1u : phase;
-        // (the timing experiment stops issuing after the first fill and so stops waiting too)
         auto wait_tile = [&](int ahead, int stage, uint32_t parity) {  // tile n_done + ahead of this warp
           if (n_done + ahead >= n_issued) return;
           if (LOADER == 1) {
-            if (nowait) return;
             cp_async_wait_pending(n_issued - n_done - ahead - 1);  // this thread's pieces of the tile ...
             __syncwarp();                                           // ... and every other lane's
           } else if (!wait_full(bar_base + 8 * stage, parity)) {
@@ -702,7 +901,6 @@ __global__ void __maxnreg__(max_regs_for(NW))
           }
         };
         auto refill = [&](int ahead, int stage) {  // the stage of tile n_done + ahead is free again
-          if (noload) return;
           __syncwarp();
           if (LOADER != 1) fence_proxy_async();  // reads of the generic proxy before writes of the async proxy
           if (run_done + ahead + STAGES < total) issue(run_done + ahead + STAGES, stage);
@@ -805,8 +1003,23 @@ __global__ void __maxnreg__(max_regs_for(NW))
           }
         }
       }
-      if (!whole && lane == 0)
-        sp.ws_hdr[2 * range + (k0 > 0 ? 0 : 1)] = ((vh * B + b) << 1) | (kend == nb ? 1 : 0);
+      if (!whole) {
+        // This part is in place: count its tiles.  The warp whose tiles complete the request merges
+        // all its parts (its own included) and writes the result; the others just go on.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          int* const cnt_b = sp.ws_cnt + (static_cast<int64_t>(vh) * B + b);
+          if (atomicAdd(cnt_b, kend - k0) + (kend - k0) == nb) {
+            *cnt_b = 0;  // nobody else touches it any more: ready for the next launch
+            // the merge itself waits until this warp has streamed all its tiles (at most two cut
+            // requests per phase end up here): no call, and nothing it would clobber, in this loop
+            int* const n_pend = reinterpret_cast<int*>(gptr(kPendCount)) + warp;
+            reinterpret_cast<int*>(gptr(kPendList))[warp * 4 + *n_pend] = vh * B + b;
+            *n_pend += 1;
+          }
+        }
+      }
       x += kend - k0;
     }
 
@@ -838,47 +1051,63 @@ __global__ void __maxnreg__(max_regs_for(NW))
         ml[warp * 4 + tig] = l_tot;
       }
       __syncthreads();
-      const int k0c = first - prefix[solo_b];
-      const bool ends = first + span == prefix[solo_b + 1];
-      const bool whole = k0c == 0 && ends;
+      const int pb = prefix[solo_b], pe = prefix[solo_b + 1];
+      const int k0c = first - pb;
+      const bool whole = k0c == 0 && first + span == pe;
       const int slot = 2 * ((cta * 2 + ph) * NW) + (k0c > 0 ? 0 : 1);  // of the CTA's first range
-      for (int idx = tid; idx < 4 * kHeadDim; idx += NW * 32) {
-        const int h = idx >> 7, d = idx & (kHeadDim - 1);
-        if (h >= nh) continue;
-        float M = -CUDART_INF_F;
+      // fold the NW records in shared memory; `final`: the result is the request's, else this CTA's part
+      auto fold = [&](const bool final) {
+        for (int idx = tid; idx < 4 * kHeadDim; idx += NW * 32) {
+          const int h = idx >> 7, d = idx & (kHeadDim - 1);
+          if (h >= nh) continue;
+          float M = -CUDART_INF_F;
 #pragma unroll
-        for (int w = 0; w < NW; ++w)
-          if (ml[w * 4 + h] > 0.f) M = fmaxf(M, mm[w * 4 + h]);
-        float den = 0.f, num = 0.f;
+          for (int w = 0; w < NW; ++w)
+            if (ml[w * 4 + h] > 0.f) M = fmaxf(M, mm[w * 4 + h]);
+          float den = 0.f, num = 0.f;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          const float lw = ml[w * 4 + h];
-          if (!(lw > 0.f)) continue;
-          const float wt = exp2f(mm[w * 4 + h] - M);
-          den += wt * lw;
-          num += wt * mo[(w * 4 + h) * kHeadDim + d];
+          for (int w = 0; w < NW; ++w) {
+            const float lw = ml[w * 4 + h];
+            if (!(lw > 0.f)) continue;
+            const float wt = exp2f(mm[w * 4 + h] - M);
+            den += wt * lw;
+            num += wt * mo[(w * 4 + h) * kHeadDim + d];
+          }
+          const int64_t row = static_cast<int64_t>(solo_b) * p.heads_q + hq0 + h;
+          if (!final) {
+            const int64_t prow = static_cast<int64_t>(slot) * 4 + h;
+            sp.ws_o[prow * kHeadDim + d] = num;
+            if (d == 0) {
+              sp.ws_m[prow] = M;
+              sp.ws_l[prow] = den;
+            }
+          } else if (p.force_partial) {
+            p.o_partial[row * kHeadDim + d] = den > 0.f ? num : 0.f;
+            if (d == 0) {
+              p.m_partial[row] = den > 0.f ? M * kLn2 : -CUDART_INF_F;
+              p.l_partial[row] = den;
+            }
+          } else {
+            const float o = den > 0.f ? num / den : 0.f;
+            store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
+            if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
+          }
         }
-        const int64_t row = static_cast<int64_t>(solo_b) * p.heads_q + hq0 + h;
-        if (!whole) {
-          const int64_t prow = static_cast<int64_t>(slot) * 4 + h;
-          sp.ws_o[prow * kHeadDim + d] = num;
-          if (d == 0) {
-            sp.ws_m[prow] = M;
-            sp.ws_l[prow] = den;
+      };
+      fold(whole);
+      if (!whole) {
+        // count this CTA's tiles; the CTA that completes the request merges its parts, every warp
+        // taking every NW-th batch of four, and folds the NW results like above
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+          int* const cnt_b = sp.ws_cnt + (static_cast<int64_t>(vh) * B + solo_b);
+          if (atomicAdd(cnt_b, span) + span == pe - pb) {
+            *cnt_b = 0;
+            reinterpret_cast<int*>(gptr(kPendCta))[ph] = vh * B + solo_b;  // merged by all warps at the end
           }
-        } else if (p.force_partial) {
-          p.o_partial[row * kHeadDim + d] = den > 0.f ? num : 0.f;
-          if (d == 0) {
-            p.m_partial[row] = den > 0.f ? M * kLn2 : -CUDART_INF_F;
-            p.l_partial[row] = den;
-          }
-        } else {
-          const float o = den > 0.f ? num / den : 0.f;
-          store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
-          if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
         }
       }
-      if (!whole && tid == 0) sp.ws_hdr[slot] = ((vh * B + solo_b) << 1) | (ends ? 1 : 0);
       __syncthreads();  // the scratch is ring space again
     }
   }
@@ -892,158 +1121,63 @@ __global__ void __maxnreg__(max_regs_for(NW))
       }
     }
   }
-}
 
-// ---- fix-up: merge the chains of partials of the requests that were cut ---------------------
-// One CTA per decode CTA looks at the 2*NW ranges of that CTA.  A range OWNS the request whose
-// first part is its slot 1; the chain continues through slot 0 of the following ranges up to
-// the part flagged last.  The four 128-thread groups of the CTA each take one owner at a time
-// (thread = output dimension, the four query heads in registers).
-constexpr int kFixThreads = 512;
-constexpr int kFixGroup = 128;
-constexpr int kFixBatch = 4;
-
-__device__ __forceinline__ void group_sync(int group) {
-  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kFixGroup) : "memory");
-}
-
-__global__ void __launch_bounds__(kFixThreads) stream_fixup_kernel(const StreamParams sp, const int ranges_per_cta,
-                                                                  const int num_ranges) {
-  const DecodeParams& p = sp.d;
-  pdl_wait();  // launched while the decode grid still runs: its writes are visible from here on
-  __shared__ int s_owner[32];
-  __shared__ int s_nown;
-  __shared__ int s_hdr[4][kFixGroup];
-  __shared__ int s_list[4][kFixGroup];
-  __shared__ int s_cnt[4], s_done[4];
-  __shared__ float s_red[3][4][4][kFixGroup];  // [M, num, den][group][head][dim]: cooperative mode only
-  const int tid = threadIdx.x, g = tid >> 7, d = tid & (kFixGroup - 1);
-  const int r0 = blockIdx.x * ranges_per_cta;
-  if (tid < 32) {  // ranges_per_cta <= 32
-    const int hd = tid < ranges_per_cta ? sp.ws_hdr[2 * (r0 + tid) + 1] : kHdrNone;
-    const unsigned mask = __ballot_sync(0xffffffffu, hd >= 0);
-    if (hd >= 0) s_owner[__popc(mask & ((1u << tid) - 1))] = r0 + tid;
-    if (tid == 0) s_nown = __popc(mask);
-  }
-  __syncthreads();
-  const int nown = s_nown;
-  const int gqa = p.heads_q / p.heads_kv;
-  // One owner in this CTA (few, long requests): all four groups share its chain, group g taking
-  // every fourth part, and the four results are merged through shared memory.  Several owners:
-  // one group per owner.
-  const bool coop = nown == 1;
-  for (int oi = coop ? 0 : g; oi < nown; oi += 4) {
-    const int range = s_owner[oi];
-    const int hd = sp.ws_hdr[2 * range + 1];
-    const int item = hd >> 1;
-    const int vh = item / p.batch, b = item - vh * p.batch;
-    const int head = vh / sp.quads, quad = vh - head * sp.quads;
-    const int nh = min(4, gqa - quad * 4);
-    float M[4], num[4], den[4];
-#pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      M[h] = -CUDART_INF_F;
-      num[h] = 0.f;
-      den[h] = 0.f;
+  // ---- the cut requests this warp / this CTA was the last to finish -------------------------
+  // Every part of them is in the workspace by now (their counters were complete).  The tile loop is
+  // over, so the call clobbers nothing that matters and the ring space is free.
+  {
+    const int hvq = quads;
+    __syncwarp();
+    const int n_pend = reinterpret_cast<const int*>(gptr(kPendCount))[warp];
+    for (int e = 0; e < n_pend; ++e) {
+      const int item = reinterpret_cast<const int*>(gptr(kPendList))[warp * 4 + e];
+      const int vh = item / B, b = item - vh * B;
+      const int head = vh / hvq, quad = vh - head * hvq;
+      merge_parts(make_io(nullptr, static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4, min(4, gqa - quad * 4)),
+                  make_plan(), vh, prefix[b], prefix[b + 1], 0, 1);
     }
-    auto merge = [&](int h, float m2, float l2, float o2) {
-      if (!(l2 > 0.f)) return;
-      const float Mn = fmaxf(M[h], m2);
-      const float a = (M[h] == -CUDART_INF_F) ? 0.f : exp2f(M[h] - Mn);
-      const float w = exp2f(m2 - Mn);
-      num[h] = num[h] * a + o2 * w;
-      den[h] = den[h] * a + l2 * w;
-      M[h] = Mn;
-    };
-    auto merge_slots = [&](const int64_t slot0, const int64_t slot1, const int64_t slot2, const int64_t slot3, int n) {
-      const int64_t slots[kFixBatch] = {slot0, slot1, slot2, slot3};
-      float m2[kFixBatch][4], l2[kFixBatch][4], o2[kFixBatch][4];
-#pragma unroll
-      for (int u = 0; u < kFixBatch; ++u)
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          const bool on = u < n && h < nh;
-          const int64_t row = slots[u] * 4 + h;
-          m2[u][h] = on ? sp.ws_m[row] : 0.f;
-          l2[u][h] = on ? sp.ws_l[row] : 0.f;
-          o2[u][h] = on ? sp.ws_o[row * kHeadDim + d] : 0.f;
-        }
-#pragma unroll
-      for (int u = 0; u < kFixBatch; ++u)
-#pragma unroll
-        for (int h = 0; h < 4; ++h) merge(h, m2[u][h], l2[u][h], o2[u][h]);
-    };
-    if (!coop || g == 0) merge_slots(2ll * range + 1, 0, 0, 0, 1);
-    const bool chain_open = (hd & 1) == 0;
-    for (int base = range + 1; chain_open && base < num_ranges; base += kFixGroup) {
-      const int r = base + d;
-      s_hdr[g][d] = r < num_ranges ? sp.ws_hdr[2 * r] : kHdrNone;
-      group_sync(g);
-      if (d == 0) {
-        int cnt = 0, done = base + kFixGroup >= num_ranges ? 1 : 0;
-        for (int j = 0; j < kFixGroup; ++j) {
-          const int hj = s_hdr[g][j];
-          if (hj < 0) continue;                        // an empty range
-          if ((hj >> 1) != item) { done = 1; break; }  // cannot happen: the chain is contiguous
-          s_list[g][cnt++] = base + j;
-          if (hj & 1) { done = 1; break; }
-        }
-        s_cnt[g] = cnt;
-        s_done[g] = done;
-      }
-      group_sync(g);
-      const int cnt = s_cnt[g];
-      const int first = coop ? g * kFixBatch : 0, stride = coop ? 4 * kFixBatch : kFixBatch;
-      for (int c0 = first; c0 < cnt; c0 += stride) {
-        const int n = min(kFixBatch, cnt - c0);
-        merge_slots(2ll * s_list[g][c0], 2ll * s_list[g][min(c0 + 1, cnt - 1)], 2ll * s_list[g][min(c0 + 2, cnt - 1)],
-                    2ll * s_list[g][min(c0 + 3, cnt - 1)], n);
-      }
-      const int done = s_done[g];
-      group_sync(g);
-      if (done) break;
-    }
-    if (coop) {  // fold the four groups' results (uniform over the CTA: one owner)
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        s_red[0][g][h][d] = M[h];
-        s_red[1][g][h][d] = num[h];
-        s_red[2][g][h][d] = den[h];
-      }
+    __syncthreads();  // every warp is through with its tiles: the ring space is free
+    for (int ph = 0; ph < 2; ++ph) {
+      const int item = reinterpret_cast<const int*>(gptr(kPendCta))[ph];
+      if (item < 0) continue;  // uniform over the CTA
+      const int vh = item / B, b = item - vh * B;
+      const int head = vh / hvq, quad = vh - head * hvq;
+      const int hq0 = head * gqa + quad * 4, nh = min(4, gqa - quad * 4);
+      // every warp merges every NW-th batch of four parts into a record o | m | l of its own ...
+      float* const rec = reinterpret_cast<float*>(gptr(kRingLoS));
+      constexpr int kRec = 4 * kHeadDim + 8;
       __syncthreads();
-      if (g != 0) continue;
+      merge_parts(make_io(rec + warp * kRec, 0, nh), make_plan(), vh, prefix[b], prefix[b + 1], warp, NW);
+      __syncthreads();
+      // ... and the CTA folds the NW records
+      for (int idx = tid; idx < 4 * kHeadDim; idx += NW * 32) {
+        const int h = idx >> 7, d = idx & (kHeadDim - 1);
+        if (h >= nh) continue;
+        float M = -CUDART_INF_F;
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        M[h] = -CUDART_INF_F;
-        num[h] = 0.f;
-        den[h] = 0.f;
+        for (int w = 0; w < NW; ++w)
+          if (rec[w * kRec + 4 * kHeadDim + 4 + h] > 0.f) M = fmaxf(M, rec[w * kRec + 4 * kHeadDim + h]);
+        float den = 0.f, num = 0.f;
 #pragma unroll
-        for (int gg = 0; gg < 4; ++gg) {
-          const float m2 = s_red[0][gg][h][d], l2 = s_red[2][gg][h][d], o2 = s_red[1][gg][h][d];
-          if (!(l2 > 0.f)) continue;
-          const float Mn = fmaxf(M[h], m2);
-          const float a = (M[h] == -CUDART_INF_F) ? 0.f : exp2f(M[h] - Mn);
-          const float w = exp2f(m2 - Mn);
-          num[h] = num[h] * a + o2 * w;
-          den[h] = den[h] * a + l2 * w;
-          M[h] = Mn;
+        for (int w = 0; w < NW; ++w) {
+          const float lw = rec[w * kRec + 4 * kHeadDim + 4 + h];
+          if (!(lw > 0.f)) continue;
+          const float wt = exp2f(rec[w * kRec + 4 * kHeadDim + h] - M);
+          den += wt * lw;
+          num += wt * rec[w * kRec + h * kHeadDim + d];
         }
-      }
-    }
-#pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      if (h >= nh) continue;
-      const int64_t row = static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4 + h;
-      if (p.force_partial) {
-        p.o_partial[row * kHeadDim + d] = den[h] > 0.f ? num[h] : 0.f;
-        if (d == 0) {
-          p.m_partial[row] = den[h] > 0.f ? M[h] * kLn2 : -CUDART_INF_F;
-          p.l_partial[row] = den[h];
+        const int64_t row = static_cast<int64_t>(b) * p.heads_q + hq0 + h;
+        if (p.force_partial) {
+          p.o_partial[row * kHeadDim + d] = den > 0.f ? num : 0.f;
+          if (d == 0) {
+            p.m_partial[row] = den > 0.f ? M * kLn2 : -CUDART_INF_F;
+            p.l_partial[row] = den;
+          }
+        } else {
+          const float o = den > 0.f ? num / den : 0.f;
+          store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
+          if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
         }
-      } else {
-        const float o = den[h] > 0.f ? num[h] / den[h] : 0.f;
-        store_out(p.out, row * kHeadDim + d, p.out_dtype, o);
-        if (p.out_f32) p.out_f32[row * kHeadDim + d] = o;
       }
     }
   }
@@ -1093,14 +1227,37 @@ __global__ void __launch_bounds__(1024) stream_prefix_kernel(const DecodeParams 
   }
 }
 
-constexpr int64_t kPartialBytes = 4 * kHeadDim * 4 + 16 + 16 + 4;  // o, m, l of four heads and the header
+constexpr int64_t kPartialBytes = 4 * kHeadDim * 4 + 16 + 16;  // o, m, l of four heads
 constexpr int64_t kPlannedPrefixBytes = (kMaxBatchPlanned + 64) * 4;  // a multiple of 256
+constexpr int64_t kCounterBytes = static_cast<int64_t>(kMaxCounters) * 4;
+constexpr int kStreamWarps = 12, kStreamStages = 3;
+
+// Byte tables of every kv head in the layout the decode kernel keeps in shared memory: block P
+// (P = 0, 1) of a head is 256 rows (one per code byte) of 64 words; word l < 32 of a row is
+// (level[low nibble], level[high nibble]) of the K group lane l uses in the QK MMAs of pair P,
+// word 32 + l the same for the V group lane l uses in the PV MMAs.
+__global__ void __launch_bounds__(256) build_byte_tables_kernel(const DecodeParams p, uint32_t* __restrict__ out) {
+  __shared__ unsigned short lv[128];  // fp16 [K|V][4][16]
+  const int head = blockIdx.x, tid = threadIdx.x;
+  if (tid < 128) {
+    const int which = tid >> 6, g = (tid >> 4) & 3, c = tid & 15;
+    lv[tid] = __half_as_ushort(__float2half_rn(which ? load_v_level(p, head, g, c) : load_k_level(p, head, g, c)));
+  }
+  __syncthreads();
+  uint32_t* const dst = out + static_cast<int64_t>(head) * (2 * kLutBlock / 4);
+  for (int e = tid; e < 2 * 256 * 64; e += 256) {
+    const int P = e >> 14, byte = (e >> 6) & 255, word = e & 63, l = word & 31;
+    const int g = word < 32 ? 2 * ((l >> 1) & 1) + P : 2 * (l >> 4) + P;
+    const unsigned short* t = lv + (word < 32 ? 0 : 64) + g * 16;
+    dst[e] = t[byte & 15] | (static_cast<uint32_t>(t[byte >> 4]) << 16);
+  }
+}
 
 // ---- tensor maps of the packed cache ------------------------------------------------------------
-// The cache is described as uint8 [page][64-byte row][64]; a box is `rows` rows of one page,
-// stored with the 64-byte swizzle.  Maps are cached per (cache, geometry, box).
+// uint8 [page][half][64-byte row][64] with the 64-byte swizzle; a box is `rows` rows of `halves`
+// halves of one page.  Maps are cached per (cache, geometry).
 struct CacheMaps {
-  CUtensorMap map16, map4, mapvs;
+  CUtensorMap code, stat, vstat;
 };
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1118,15 +1275,16 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-bool make_cache_map(CUtensorMap* out, const DecodeParams& p, int rows) {
+bool make_half_map(CUtensorMap* out, const DecodeParams& p, int rows, int halves) {
   const EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return false;
   const PageGeom geo = make_geom(p.block_size, p.heads_kv);
-  const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(geo.block_i32) * 4 / 64, static_cast<cuuint64_t>(p.num_pages)};
-  const cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(p.page_stride) * 4};
-  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(rows), 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint32_t*>(p.cache), dims, strides, box, estr,
+  const cuuint64_t half_bytes = static_cast<cuuint64_t>(geo.block_i32) * 2;  // K codes + K statistics
+  const cuuint64_t dims[4] = {64, half_bytes / 64, 2, static_cast<cuuint64_t>(p.num_pages)};
+  const cuuint64_t strides[3] = {64, half_bytes, static_cast<cuuint64_t>(p.page_stride) * 4};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(rows), static_cast<cuuint32_t>(halves), 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint32_t*>(p.cache), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -1145,7 +1303,7 @@ bool make_vstat_map(CUtensorMap* out, const DecodeParams& p) {
              CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// false: the driver offers no tensor maps for this cache (then the cp.async loader is used)
+// false: the driver offers no tensor maps for this cache
 bool cache_maps_for(const DecodeParams& p, CacheMaps* out) {
   struct Entry {
     const void* cache;
@@ -1169,15 +1327,56 @@ bool cache_maps_for(const DecodeParams& p, CacheMaps* out) {
   Entry& e = slots[next];
   next = (next + 1) % 8;
   e = Entry{p.cache, p.num_pages, p.page_stride, p.block_size, p.heads_kv, dev, {}, false};
-  e.ok = (p.page_stride * 4) % 64 == 0 && make_cache_map(&e.maps.map16, p, 16) && make_cache_map(&e.maps.map4, p, 4) &&
-         make_vstat_map(&e.maps.mapvs, p);
+  const bool one_tile_pages = p.block_size == kTile;
+  // half a page must be a whole number of 64-byte rows and start on a 16-byte boundary
+  e.ok = (p.page_stride * 4) % 64 == 0 && (static_cast<int64_t>(p.heads_kv) * p.block_size) % 4 == 0 &&
+         make_half_map(&e.maps.code, p, 16, 2) && make_half_map(&e.maps.stat, p, 4, one_tile_pages ? 2 : 1) &&
+         make_vstat_map(&e.maps.vstat, p);
   *out = e.maps;
   return e.ok;
 }
 
-template <int NW, int STAGES, int LOADER, int PAIR = 2>
-int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_seq_len, int sm_count,
-                   cudaStream_t stream) {
+int device_sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && cached[dev]) return cached[dev];
+  int n = 0;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (dev < 64) cached[dev] = n;
+  return n;
+}
+
+// grid size and share policy of a launch: the same numbers on the host (launch, self-test) and,
+// through StreamParams, on the device
+void plan_launch(int hv, int batch, int max_seq_len, int sm_count, part::Plan* pl) {
+  const int NW = kStreamWarps;
+  const int64_t tiles_max = static_cast<int64_t>(hv) * batch * ((max_seq_len + kTile - 1) / kTile);
+  int64_t ctas = (tiles_max + 2 * NW - 1) / (2 * NW);
+  if (ctas < hv) ctas = hv;  // a share never spans more than two heads
+  if (ctas > sm_count) ctas = sm_count;
+  const int C = static_cast<int>(ctas);
+  // Equal shares make the CTAs whose share straddles two heads set up twice and restart their
+  // pipelines (a few us, which the share computation takes off their tile count); head-aligned
+  // shares avoid that but the heads served by fewer CTAs finish later.  Take the cheaper of the
+  // two estimates (0.1 us per tile and SM).
+  const int base = C / hv;
+  const double per_cta_us = static_cast<double>(tiles_max) / C * 0.1;
+  const double aligned_loss_us = per_cta_us * (static_cast<double>(C) / hv / base - 1.0);
+  // compensated equal shares lose about (heads - 1) gaps spread over all CTAs
+  const double equal_loss_us = 4.0 * (hv - 1) / C + 1.0;
+  pl->C = C;
+  pl->NW = NW;
+  pl->hv = hv;
+  pl->Tb = 0;  // known on the device only
+  pl->gap = 40;  // ~4 us: with 100 the straddling CTAs were measured to finish 7 us early
+  pl->aligned = (C % hv == 0 || aligned_loss_us < equal_loss_us) ? 1 : 0;
+}
+
+template <int LOADER>
+int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, const void* byte_tables, int max_seq_len,
+                   int sm_count, cudaStream_t stream) {
+  constexpr int NW = kStreamWarps, STAGES = kStreamStages;
   using R = Ring<NW, STAGES>;
   StreamParams sp;
   sp.d = p;
@@ -1186,36 +1385,23 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
   sp.q_vec = (p.q_dtype == BKV_BF16 || p.q_dtype == BKV_F16) && reinterpret_cast<uintptr_t>(p.q) % 8 == 0 &&
              p.q_batch_stride % 4 == 0;
   const int hv = p.heads_kv * sp.quads;
-  if (hv > sm_count) return BKV_ERR_UNSUPPORTED;
-  const int64_t tiles_max = static_cast<int64_t>(hv) * p.batch * ((max_seq_len + kTile - 1) / kTile);
-  int64_t ctas = (tiles_max + 2 * NW - 1) / (2 * NW);
-  if (ctas < hv) ctas = hv;  // a share never spans more than two heads
-  if (ctas > sm_count) ctas = sm_count;
-  const int C = static_cast<int>(ctas);
-  // Equal shares make the CTAs whose share straddles two heads build the tables twice and
-  // restart their pipelines (a few us, which the share computation takes off their tile
-  // count); head-aligned shares avoid that but the heads served by fewer CTAs finish later.
-  // Take the cheaper of the two estimates (0.1 us per tile and SM).
-  {
-    const int base = C / hv;
-    const double per_cta_us = static_cast<double>(tiles_max) / C * 0.1;
-    const double aligned_loss_us = per_cta_us * (static_cast<double>(C) / hv / base - 1.0);
-    sp.straddle_tiles = 40;  // ~4 us: with 100 the straddling CTAs were measured to finish 7 us early
-    // compensated equal shares lose about (heads - 1) gaps spread over all CTAs
-    const double equal_loss_us = 4.0 * (hv - 1) / C + 1.0;
-    sp.aligned = (C % hv == 0 || aligned_loss_us < equal_loss_us) ? 1 : 0;
-    if (p.flags & BKV_FLAG_DEBUG_EQUAL_SHARES) sp.aligned = 0;
-    if (p.flags & BKV_FLAG_DEBUG_ALIGNED_SHARES) sp.aligned = 1;
-  }
-  const int num_ranges = C * 2 * NW;
-  const int64_t slots = 2ll * num_ranges;
-  if (!ws || ws_bytes < slots * kPartialBytes + kPlannedPrefixBytes) return BKV_ERR_ARG;
-  char* w = static_cast<char*>(ws) + kPlannedPrefixBytes;  // the prefix sums come first
+  if (hv > sm_count || sm_count > kMaxCtas) return BKV_ERR_UNSUPPORTED;
+  if (static_cast<int64_t>(hv) * p.batch > kMaxCounters) return BKV_ERR_UNSUPPORTED;
+  part::Plan pl;
+  plan_launch(hv, p.batch, max_seq_len, sm_count, &pl);
+  const int C = pl.C;
+  sp.aligned = pl.aligned;
+  sp.straddle_tiles = pl.gap;
+  sp.byte_tables = static_cast<const uint32_t*>(byte_tables);
+  const int64_t slots = 2ll * C * 2 * NW;
+  if (!ws || ws_bytes < kPlannedPrefixBytes + kCounterBytes + slots * kPartialBytes) return BKV_ERR_ARG;
+  char* w = static_cast<char*>(ws);  // the prefix sums come first, then the counters, then the partials
+  sp.ws_prefix = reinterpret_cast<int*>(w);
+  sp.ws_cnt = reinterpret_cast<int*>(w + kPlannedPrefixBytes);
+  w += kPlannedPrefixBytes + kCounterBytes;
   sp.ws_o = reinterpret_cast<float*>(w);
   sp.ws_m = reinterpret_cast<float*>(w + slots * (4 * kHeadDim * 4));
   sp.ws_l = sp.ws_m + slots * 4;
-  sp.ws_hdr = reinterpret_cast<int*>(sp.ws_l + slots * 4);
-  sp.ws_prefix = static_cast<int*>(ws);
   if (p.batch > kMaxBatch) {
     stream_prefix_kernel<<<1, 1024, 0, stream>>>(p, sp.ws_prefix);
     const int rcp = check_launch("bkv_decode_stream_sm100(prefix)");
@@ -1224,8 +1410,7 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
 
   CacheMaps maps = {};
   if (LOADER == 3 && !cache_maps_for(p, &maps)) return BKV_ERR_UNSUPPORTED;
-  auto kern = p.stat_bf16 ? decode_stream_kernel<NW, STAGES, true, LOADER, PAIR>
-                          : decode_stream_kernel<NW, STAGES, false, LOADER, PAIR>;
+  auto kern = p.stat_bf16 ? decode_stream_kernel<NW, STAGES, true, LOADER> : decode_stream_kernel<NW, STAGES, false, LOADER>;
   static bool configured[2][64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1238,9 +1423,8 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
       set_last_cuda_error(e, "cudaFuncSetAttribute(decode_stream_kernel)");
       return BKV_ERR_CUDA;
     }
-    // the small kernels around the decode grid ask for the same shared-memory carve-out, so the
-    // SMs are not reconfigured between the launches of a step
-    cudaFuncSetAttribute(stream_fixup_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    // the planning kernel asks for the same shared-memory carve-out, so the SMs are not
+    // reconfigured between the launches of a step
     cudaFuncSetAttribute(stream_prefix_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured[p.stat_bf16 ? 1 : 0][dev] = true;
   }
@@ -1259,72 +1443,145 @@ int launch_variant(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_se
     dattr[0].val.programmaticStreamSerializationAllowed = 1;
     dcfg.attrs = dattr;
     dcfg.numAttrs = 1;
-    const cudaError_t de = cudaLaunchKernelEx(&dcfg, kern, sp, maps.map16, maps.map4, maps.mapvs);
+    const cudaError_t de = cudaLaunchKernelEx(&dcfg, kern, sp, maps.code, maps.stat, maps.vstat);
     if (de != cudaSuccess) {
       set_last_cuda_error(de, "bkv_decode_stream_sm100(decode, dependent launch)");
       return BKV_ERR_CUDA;
     }
   } else {
-    kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp, maps.map16, maps.map4, maps.mapvs);
+    kern<<<C, NW * 32, R::kDynBytes, stream>>>(sp, maps.code, maps.stat, maps.vstat);
   }
-  int rc = check_launch("bkv_decode_stream_sm100(decode)");
-  if (rc != BKV_OK) return rc;
-  // programmatic dependent launch: the fix-up grid is set up while the decode grid drains
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(C);
-  cfg.blockDim = dim3(kFixThreads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, stream_fixup_kernel, sp, 2 * NW, num_ranges);
-  if (e != cudaSuccess) {
-    set_last_cuda_error(e, "bkv_decode_stream_sm100(fixup)");
-    return BKV_ERR_CUDA;
-  }
-  return BKV_OK;
-}
-
-int device_sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && cached[dev]) return cached[dev];
-  int n = 0;
-  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  if (dev < 64) cached[dev] = n;
-  return n;
+  return check_launch("bkv_decode_stream_sm100(decode)");
 }
 
 }  // namespace
 
 int64_t stream_workspace_bytes() {
   const int64_t sms = device_sm_count();
-  // the prefix sums, then the ranges of the widest configuration (16 warps), two slots each
-  return kPlannedPrefixBytes + sms * 2 * 16 * 2 * kPartialBytes;
+  // the prefix sums, the request counters, then two slots for each of the 2 * warps ranges of a CTA
+  return kPlannedPrefixBytes + kCounterBytes + sms * 2 * kStreamWarps * 2 * kPartialBytes;
 }
 
-int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, int max_seq_len, cudaStream_t stream,
-                         int config) {
+int init_stream_workspace(void* ws, int64_t ws_bytes, cudaStream_t stream) {
+  if (!ws || ws_bytes < kPlannedPrefixBytes + kCounterBytes) return BKV_ERR_ARG;
+  const cudaError_t e = cudaMemsetAsync(static_cast<char*>(ws) + kPlannedPrefixBytes, 0, kCounterBytes, stream);
+  if (e != cudaSuccess) {
+    set_last_cuda_error(e, "bkv_decode_stream_workspace_init");
+    return BKV_ERR_CUDA;
+  }
+  return BKV_OK;
+}
+
+int64_t byte_table_bytes(int heads_kv) { return static_cast<int64_t>(heads_kv) * 2 * kLutBlock; }
+
+int launch_build_byte_tables(const DecodeParams& p, void* out, cudaStream_t stream) {
+  if (!aligned16(out)) return BKV_ERR_ALIGN;
+  build_byte_tables_kernel<<<p.heads_kv, 256, 0, stream>>>(p, static_cast<uint32_t*>(out));
+  return check_launch("bkv_decode_tables_sm100");
+}
+
+int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, const void* byte_tables, int max_seq_len,
+                         cudaStream_t stream, int config) {
   const int r = p.block_size / kTile;
   if (p.block_size % kTile != 0 || (r & (r - 1)) != 0 || p.block_size > 1024) return BKV_ERR_UNSUPPORTED;
   if ((p.page_stride * 4) % 16 != 0 || !aligned16(p.cache)) return BKV_ERR_UNSUPPORTED;
   if (p.token_lo % p.block_size != 0) return BKV_ERR_UNSUPPORTED;
   if (p.batch > kMaxBatchPlanned || p.num_pages > (1ll << kMaxPagesLog2)) return BKV_ERR_UNSUPPORTED;
+  // the byte tables hold fp16 levels: 16-bit level tables convert exactly, float32 ones would be rounded
+  if (p.table_dtype == BKV_F32) return BKV_ERR_UNSUPPORTED;
+  if (byte_tables && !aligned16(byte_tables)) return BKV_ERR_ALIGN;
+  // merged results leave in 16-byte pieces; the partials are read back in 16-byte pieces
+  if (!aligned16(ws) || (p.out && !aligned16(p.out)) || (p.out_f32 && !aligned16(p.out_f32))) return BKV_ERR_ALIGN;
   const int sms = device_sm_count();
   if (sms <= 0) return BKV_ERR_CUDA;
-  switch (config) {
-    case 1: return launch_variant<8, 4, 3>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 2: return launch_variant<12, 3, 3>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 3: return launch_variant<16, 2, 3>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 5: return launch_variant<12, 3, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 6: return launch_variant<8, 4, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    case 7: return launch_variant<16, 2, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
-    default: return launch_variant<12, 3, 1>(p, ws, ws_bytes, max_seq_len, sms, stream);
+  if (config == 1) return launch_variant<3>(p, ws, ws_bytes, byte_tables, max_seq_len, sms, stream);
+  return launch_variant<1>(p, ws, ws_bytes, byte_tables, max_seq_len, sms, stream);
+}
+
+// Host-side check of the work partition (no device access): for `batch` requests of the given tile
+// counts, walk every warp's run exactly as the kernel does, note which slot every part of every cut
+// request goes to, and compare that with the list the merging warp derives.  Returns the number of
+// requests whose lists differ, or -1 for unusable arguments.
+int check_partition(const int* tiles, int batch, int hv, int sm_count, int max_tiles_per_request) {
+  if (!tiles || batch <= 0 || hv <= 0 || sm_count < hv || max_tiles_per_request <= 0) return -1;
+  part::Plan pl;
+  plan_launch(hv, batch, max_tiles_per_request * kTile, sm_count, &pl);
+  std::vector<int64_t> prefix(batch + 1, 0);
+  for (int b = 0; b < batch; ++b) {
+    if (tiles[b] < 0 || tiles[b] > max_tiles_per_request) return -1;
+    prefix[b + 1] = prefix[b] + tiles[b];
   }
+  if (prefix[batch] > INT32_MAX) return -1;
+  pl.Tb = static_cast<int>(prefix[batch]);
+  // what the kernel writes: (virtual head, request) -> slots, tiles counted
+  std::vector<std::vector<int>> written(static_cast<size_t>(hv) * batch);
+  std::vector<int64_t> counted(static_cast<size_t>(hv) * batch, 0);
+  int64_t covered = 0;
+  for (int c = 0; c < pl.C; ++c) {
+    int64_t ga, gb;
+    part::share_of(pl, c, &ga, &gb);
+    covered += gb - ga;
+    for (int ph = 0; ph < 2; ++ph) {
+      const part::Span s = part::phase_span(pl, ga, gb, ph);
+      if (s.span == 0) continue;
+      if (s.vh >= hv) return -1;
+      auto request_of = [&](int x) {
+        int l = 0, h = batch;
+        while (h - l > 1) {
+          const int mid = (l + h) >> 1;
+          if (prefix[mid] <= x) l = mid; else h = mid;
+        }
+        return l;
+      };
+      const int solo_b = request_of(s.first);
+      if (prefix[solo_b + 1] >= s.first + s.span) {  // one partial for the CTA
+        const bool whole = s.first == prefix[solo_b] && s.first + s.span == prefix[solo_b + 1];
+        if (!whole) {
+          written[static_cast<size_t>(s.vh) * batch + solo_b].push_back(2 * ((c * 2 + ph) * pl.NW) + (s.first > prefix[solo_b] ? 0 : 1));
+          counted[static_cast<size_t>(s.vh) * batch + solo_b] += s.span;
+        }
+        continue;
+      }
+      for (int w = 0; w < pl.NW; ++w) {
+        const int wa = part::run_begin(s, pl.NW, w), wb = part::run_begin(s, pl.NW, w + 1);
+        int x = wa;
+        int b = wb > wa ? request_of(wa) : 0;
+        while (x < wb) {
+          while (prefix[b + 1] <= x) ++b;
+          const int pb = static_cast<int>(prefix[b]), nb = static_cast<int>(prefix[b + 1] - prefix[b]);
+          const int k0 = x - pb, kend = std::min(nb, wb - pb);
+          if (!(k0 == 0 && kend == nb)) {
+            written[static_cast<size_t>(s.vh) * batch + b].push_back(2 * ((c * 2 + ph) * pl.NW + w) + (k0 > 0 ? 0 : 1));
+            counted[static_cast<size_t>(s.vh) * batch + b] += kend - k0;
+          }
+          x += kend - k0;
+        }
+      }
+    }
+  }
+  int bad = covered == static_cast<int64_t>(hv) * pl.Tb ? 0 : 1;
+  for (int vh = 0; vh < hv; ++vh)
+    for (int b = 0; b < batch; ++b) {
+      const std::vector<int>& w = written[static_cast<size_t>(vh) * batch + b];
+      if (w.empty()) continue;
+      const int pb = static_cast<int>(prefix[b]), pe = static_cast<int>(prefix[b + 1]);
+      std::vector<int> derived;
+      int c_lo, c_hi;
+      part::ctas_near_head(pl, vh, &c_lo, &c_hi);
+      for (int c = c_lo; c <= c_hi; ++c) {
+        int64_t sa, sb;
+        part::share_of(pl, c, &sa, &sb);
+        const part::CtaParts cp = part::cta_parts(pl, sa, sb, vh, pb, pe);
+        bool first_of_cta = true;
+        for (int wi = 0; wi < pl.NW; ++wi) {
+          if (!((cp.mask >> wi) & 1u)) continue;
+          derived.push_back(part::part_slot(pl, c, cp.ph, cp.solo ? 0 : wi, cp.starts && first_of_cta));
+          first_of_cta = false;
+        }
+      }
+      if (derived != w || counted[static_cast<size_t>(vh) * batch + b] != pe - pb) ++bad;
+    }
+  return bad;
 }
 
 int read_stream_status() {

@@ -1,4 +1,4 @@
-// PTX wrappers and the shared-memory tile format used by the tensor-core decode kernels.
+// PTX wrappers and the shared-memory map used by the tensor-core decode kernel.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -8,20 +8,7 @@
 namespace bkv {
 namespace mma {
 
-// ---- one 16-token tile of one KV head in a ring slot of the split-grid kernel -------------
-// K codes (16 x 64 B), K statistics (16 x 16 B), V codes (16 x 64 B), V statistics
-// (4 groups x 16 tokens x 4 B).  The code rows of tokens 8-15 start kCodeSkew bytes later
-// than contiguous, which makes the per-lane code loads of the MMA layouts conflict-free.
-// (The persistent kernel uses a swizzled slot instead, see bkv_decode_stream.cu.)
-constexpr int kTile = 16;
-constexpr int kCodeSkew = 16;
-constexpr int kOffKLo = 0;
-constexpr int kOffKHi = 512 + kCodeSkew;
-constexpr int kOffKStat = kOffKHi + 512;
-constexpr int kOffVLo = kOffKStat + 256;
-constexpr int kOffVHi = kOffVLo + 512 + kCodeSkew;
-constexpr int kOffVStat = kOffVHi + 512;
-constexpr int kTileBytes = kOffVStat + 256;  // 2592
+constexpr int kTile = 16;  // tokens of one tile: the M of the QK MMA and the K of the PV MMA
 
 // ---- shared-memory map of a CTA that owns the SM ---------------------------------------
 constexpr uint32_t kSmemBase = 0x400;              // dynamic shared memory starts after the 1 KB the system reserves
@@ -29,16 +16,9 @@ constexpr uint32_t kSmemEnd = kSmemBase + 232448;  // 227 KB opt-in maximum
 constexpr uint32_t kLutAddr = 0x10000;  // table block P at kLutAddr + P*kLutBlock: address = block | byte << 8 | slot
 constexpr uint32_t kLutBlock = 0x10000;
 constexpr uint32_t kRingHi = kLutAddr + 2 * kLutBlock;
-constexpr int kCtrlBytes = 2048;  // barriers, fp16 level tables
-constexpr uint32_t kRingLo = kSmemBase + kCtrlBytes;
-constexpr int kLoSlots = (kLutAddr - kRingLo) / kTileBytes;
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait that lasts 2 s gives up
 constexpr float kRescaleThreshold = 8.f;                     // log2 units: p stays below 2^8
-// token held by k-slot n of the PV MMAs (nibble n): 0,1,3,2, 8,9,11,10, 4,5,7,6, 12,13,15,14
-constexpr unsigned long long kTokOfSlot = 0xEFDC6754AB982310ull;
-// QK MMA row g (and g+8) carries the token of k-slot kRowSlot[g] (and +8): 0,1,4,5,2,3,6,7 (an involution)
-constexpr uint32_t kRowSlot = 0x76325410u;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -148,6 +128,11 @@ __device__ __forceinline__ float fast_exp2(float x) {  // ex2.approx: 2 ulp, exp
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {  // a*b + c, rounded once
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
   return r;
 }
 // Table look-up: the address is complete, no base is added.  Not volatile: the table is

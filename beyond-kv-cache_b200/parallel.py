@@ -68,10 +68,7 @@ def _stream_workspace(device: torch.device) -> torch.Tensor:
     key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
     ws = _WORKSPACES.get(key)
     if ws is None:
-        with torch.cuda.device(device):
-            nbytes = int(_lib.load().bkv_decode_stream_workspace_bytes())
-        ws = torch.empty((nbytes,), dtype=torch.uint8, device=device)
-        _WORKSPACES[key] = ws
+        ws = _WORKSPACES[key] = _lib.stream_workspace(device)
     return ws
 
 
@@ -100,7 +97,9 @@ def decode_range_partial(
     if q_points_k.dtype != q_points_v.dtype:
         q_points_k, q_points_v = q_points_k.float(), q_points_v.float()
     stat = stat_dtype if stat_dtype is not None else q.dtype
-    if batch <= 16384 and int(cache.shape[0]) <= (1 << 26) and layout.block_size in (16, 32, 64, 128):
+    quads = (heads_q // int(layout.num_kv_heads) + 3) // 4
+    if (batch <= 16384 and int(cache.shape[0]) <= (1 << 26) and layout.block_size in (16, 32, 64, 128)
+            and int(layout.num_kv_heads) * quads * batch <= (1 << 20) and q_points_k.dtype != torch.float32):
         # persistent schedule: every SM works on the range even when it is one request's
         _lib.call(
             "bkv_decode_range_stream_sm100",
@@ -110,7 +109,7 @@ def decode_range_partial(
             block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
             q_points_k.contiguous().data_ptr(), q_points_v.contiguous().data_ptr(), _lib.dtype_code(q_points_k.dtype),
             o.data_ptr(), m.data_ptr(), l.data_ptr(), _stream_workspace(q.device).data_ptr(),
-            int(_stream_workspace(q.device).numel()), batch, heads_q, int(token_lo), int(token_hi),
+            int(_stream_workspace(q.device).numel()), None, batch, heads_q, int(token_lo), int(token_hi),
             float(softmax_scale), 0, 0, _lib.current_stream(q.device),
         )
         return o, m, l
@@ -171,7 +170,7 @@ def decode_kv_range_split(
         int(layout.num_kv_heads), _lib.dtype_code(stat),
         block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
         q_points_k.contiguous().data_ptr(), q_points_v.contiguous().data_ptr(), _lib.dtype_code(q_points_k.dtype),
-        o.data_ptr(), m.data_ptr(), l.data_ptr(), ws.data_ptr(), int(ws.numel()), batch, heads_q,
+        o.data_ptr(), m.data_ptr(), l.data_ptr(), ws.data_ptr(), int(ws.numel()), None, batch, heads_q,
         int(token_lo), int(token_hi), float(softmax_scale), 0, 0, _lib.current_stream(q.device),
     )
     if world > 1:

@@ -12,13 +12,16 @@ Kept from the reference interface (file:line in the reference project):
 * ``make_uniform_q_points`` / ``make_uniform_thresholds`` (:75-93)
 * ``prepare_qpoints_and_thresholds`` (:116-195)
 * ``pack_codes`` / ``unpack_codes`` (:358-431) — format helpers, any device
+* ``PackedK`` / ``PackedV`` (:290-335), ``quantize_k`` / ``quantize_v`` (:439-486, :525-584),
+  ``dequantize_k`` / ``dequantize_v`` (:489-517, :587-616) — here evaluated by the encode and
+  read-back kernels (CUDA tensors only)
 * ``PagedLayout.build`` / ``build_hnd`` (:629-786)
 * ``write_tokens_to_paged_cache`` (:2147-2207)
 * ``dequantize_paged_kv_to_dense`` (:1703-1856)
 * ``read_request_from_paged_cache`` (:2210-2395) — here served by the read-back kernel
 
-The numerical oracles of the reference module (``quantize_k``, ``dequantize_k`` …)
-are test infrastructure and live outside this package.
+A CPU restatement of the same arithmetic exists as test infrastructure outside this package;
+nothing here falls back to it.
 """
 
 from __future__ import annotations
@@ -39,8 +42,6 @@ SUPPORTED_CODE_LAYOUTS = (CODE_LAYOUT_HEAD_WORD_TOKEN, CODE_LAYOUT_HND_TOKEN_WOR
 
 _HEAD_DIM = 128
 _UNIFORM_TABLES: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}
-_DERIVED_THRESHOLDS: dict[tuple, torch.Tensor] = {}
-_SORTED_TABLES: dict[tuple, bool] = {}
 
 
 # --------------------------------------------------------------------------- tables
@@ -102,12 +103,14 @@ def prepare_qpoints_and_thresholds(
         raise ValueError("thresholds are required for grouped q_points")
     if uniform_thr is not None:
         return qp, uniform_thr
-    tkey = (qp.data_ptr(), key, qp.numel(), qp._version)
-    thr = _DERIVED_THRESHOLDS.get(tkey)
-    if thr is None:
-        thr = make_uniform_thresholds(qp.to(torch.float32)).to(dtype=qp.dtype).contiguous()
-        _DERIVED_THRESHOLDS[tkey] = thr
-    return qp, thr
+    # mid-point thresholds of a caller's shared table: kept ON that tensor (with the version
+    # they were derived from), never in a table keyed by its address, which a later tensor
+    # could inherit
+    held = getattr(qp, "_bkv_midpoints", None)
+    if held is None or held[0] != qp._version:
+        held = (qp._version, make_uniform_thresholds(qp.to(torch.float32)).to(dtype=qp.dtype).contiguous())
+        qp._bkv_midpoints = held
+    return qp, held[1]
 
 
 def _validate_real_quant_params(num_bits: int, group_size: int) -> None:
@@ -269,20 +272,28 @@ def _stat_dtype_from_model_dtype(dtype: torch.dtype) -> torch.dtype:
 # --------------------------------------------------------------------------- helpers
 def _tables_sorted(thr: torch.Tensor) -> bool:
     """True when every threshold table is non-decreasing (binary search is then
-    identical to the reference's count).  The answer is cached per tensor version;
-    during stream capture an unknown table is treated as unsorted."""
-    key = (thr.data_ptr(), tuple(thr.shape), thr.dtype, thr._version)
-    known = _SORTED_TABLES.get(key)
-    if known is not None:
-        return known
-    if torch.cuda.is_current_stream_capturing():
+    identical to the reference's count).  The answer is kept on the tensor object itself,
+    tagged with the tensor version it was computed for, so it can never be inherited by
+    another table that the allocator later places at the same address.  Finding it out costs
+    one device read; during stream capture an unclassified table is treated as unsorted
+    (the counting search is always right, only slower)."""
+    held = getattr(thr, "_bkv_sorted", None)
+    if held is not None and held[0] == thr._version:
+        return held[1]
+    if thr.is_cuda and torch.cuda.is_current_stream_capturing():
         return False
-    if len(_SORTED_TABLES) > 256:
-        _SORTED_TABLES.clear()
     t = thr.float()
     known = bool((t[..., 1:] >= t[..., :-1]).all().item())
-    _SORTED_TABLES[key] = known
+    thr._bkv_sorted = (thr._version, known)
     return known
+
+
+def classify_tables(*thresholds: torch.Tensor) -> None:
+    """Classify threshold tables now (one device read each), so that later writes through
+    :func:`write_tokens_to_paged_cache` with these very tensors cost no host synchronisation."""
+    for thr in thresholds:
+        if thr is not None:
+            _tables_sorted(thr)
 
 
 def _layout_code(layout: PagedLayout) -> int:
@@ -446,40 +457,26 @@ def dequantize_paged_kv_to_dense(
     are bit-identical to ``read_request_from_paged_cache``."""
     if not cache.is_cuda:
         raise RuntimeError("packed chunked-prefill dequantization requires CUDA")
-    if (
-        cache.dtype != torch.int32
-        or cache.dim() != 2
-        or not cache.is_contiguous()
-        or block_table.device != cache.device
-        or seq_lens.device != cache.device
-        or seq_start_loc.device != cache.device
-        or block_table.dtype != torch.int32
-        or seq_lens.dtype != torch.int32
-        or seq_start_loc.dtype != torch.int32
-        or block_table.dim() != 2
-        or seq_lens.dim() != 1
-        or seq_start_loc.dim() != 1
-        or int(seq_start_loc.numel()) != int(seq_lens.numel()) + 1
-        or layout.bits != 4
-        or layout.head_dim != _HEAD_DIM
-        or layout.k_group_size != 32
-        or layout.v_group_size != 32
-        or layout.code_layout != CODE_LAYOUT_HND_TOKEN_WORD
-        or int(cache.shape[1]) != int(layout.block_i32)
-        or block_table.stride(1) != 1
-    ):
+    int32_on_cache = lambda t, rank: t.device == cache.device and t.dtype == torch.int32 and t.dim() == rank  # noqa: E731
+    cache_abi_ok = (
+        cache.dtype == torch.int32 and cache.dim() == 2 and cache.is_contiguous(),
+        int32_on_cache(block_table, 2) and block_table.stride(-1) == 1,
+        int32_on_cache(seq_lens, 1),
+        int32_on_cache(seq_start_loc, 1) and int(seq_start_loc.numel()) == int(seq_lens.numel()) + 1,
+        (layout.bits, layout.head_dim, layout.k_group_size, layout.v_group_size) == (4, _HEAD_DIM, 32, 32),
+        layout.code_layout == CODE_LAYOUT_HND_TOKEN_WORD,
+        cache.dim() == 2 and int(cache.shape[1]) == int(layout.block_i32),
+    )
+    if not all(cache_abi_ok):
         raise ValueError("unsupported packed chunked-prefill cache ABI")
-    if (
-        out_k.device != cache.device
-        or out_v.device != cache.device
-        or out_k.dtype not in (torch.float16, torch.bfloat16, torch.float32)
-        or out_v.dtype != out_k.dtype
-        or out_k.dim() != 3
-        or tuple(out_v.shape) != tuple(out_k.shape)
-        or tuple(out_k.shape[1:]) != (layout.num_kv_heads, _HEAD_DIM)
-        or not out_k.is_contiguous()
-        or not out_v.is_contiguous()
-    ):
+    outputs_ok = (
+        out_k.device == cache.device and out_v.device == cache.device,
+        out_k.dtype in (torch.float16, torch.bfloat16, torch.float32) and out_v.dtype == out_k.dtype,
+        out_k.dim() == 3 and tuple(out_v.shape) == tuple(out_k.shape),
+        tuple(out_k.shape[1:]) == (layout.num_kv_heads, _HEAD_DIM),
+        out_k.is_contiguous() and out_v.is_contiguous(),
+    )
+    if not all(outputs_ok):
         raise ValueError("dense chunked-prefill outputs must be contiguous FP16/BF16 HND tensors")
     max_seq_len = int(max_seq_len)
     if max_seq_len <= 0:
@@ -533,3 +530,161 @@ def read_request_from_paged_cache(
             stat_dtype=stat_dtype if stat_dtype is not None else out_dtype,
         )
     return out_k.unsqueeze(0), out_v.unsqueeze(0)
+
+
+# --------------------------------------------------------------------------- dense quantiser API
+@dataclass
+class PackedK:
+    """Packed K state (reference :290-312): ``codes`` uint8 ``(B, S, H, D//G, G)``, ``packed``
+    uint32 ``(B, S, H, D//G, 4)``, ``mn`` / ``scale`` 16-bit ``(B, S, H, D//G)``."""
+
+    codes: torch.Tensor
+    packed: torch.Tensor
+    mn: torch.Tensor
+    scale: torch.Tensor
+    bits: int
+    group_size: int
+    pack_token_last: bool = False
+
+
+@dataclass
+class PackedV:
+    """Packed V state (reference :315-335); with ``pack_token_last`` the token axis is the
+    innermost one: ``packed`` ``(B, H, D//G, 4, S)``, ``mn`` / ``scale`` ``(B, H, D//G, S)``."""
+
+    codes: torch.Tensor
+    packed: torch.Tensor
+    mn: torch.Tensor
+    scale: torch.Tensor
+    bits: int
+    group_size: int
+    pack_token_last: bool = False
+
+
+_SCRATCH_BLOCK = 16  # page size of the private page pool the dense entry points run through
+
+
+def _quantize_rows(x, num_bits, group_size, q_points, thresholds, stat_dtype):
+    """Shared body of quantize_k / quantize_v (their arithmetic is the same, reference
+    :463-475 and :552-564): the rows go through the encode-on-write kernel into a private page
+    pool with consecutive slots, and the K regions of those pages are read back as the dense
+    ``packed`` / ``scale`` / ``mn`` tensors."""
+    _validate_real_quant_params(num_bits, group_size)
+    if x.dim() != 4:
+        raise ValueError("expected x.shape=(B, S, H, D)")
+    B, S, H, D = (int(n) for n in x.shape)
+    if D % group_size != 0:
+        raise ValueError(f"head_dim {D} not divisible by group_size {group_size}")
+    stat_dtype = _stat_dtype_from_model_dtype(stat_dtype or x.dtype)
+    if not x.is_cuda:
+        raise RuntimeError("quantize_k / quantize_v run on the sm_100a encode kernel: x must be a CUDA tensor")
+    if D != _HEAD_DIM:
+        raise RuntimeError(f"the sm_100a encode kernel handles head_dim {_HEAD_DIM}, got {D}")
+    qp, thr = prepare_qpoints_and_thresholds(num_bits=num_bits, device=x.device, q_points=q_points, thresholds=thresholds)
+    groups, tokens, bs = D // group_size, B * S, _SCRATCH_BLOCK
+    pages = max(1, (tokens + bs - 1) // bs)
+    layout = PagedLayout.build_hnd(bs, H, D, 4, group_size, group_size)
+    cache = torch.zeros((pages, layout.block_i32), dtype=torch.int32, device=x.device)
+    rows = x.reshape(tokens, H, D)
+    if rows.stride(2) != 1:
+        rows = rows.contiguous()
+    if tokens:
+        slots = torch.arange(tokens, dtype=torch.int64, device=x.device)
+        write_tokens_to_paged_cache(cache, layout, None, slots, rows, rows, q_points_k=qp, q_points_v=qp,
+                                    thresholds_k=thr, thresholds_v=thr, require_fast=True, stat_dtype=stat_dtype)
+    code_words, stat_words = H * bs * 16, H * bs * groups
+    packed = cache[:, :code_words].reshape(pages, H, bs, groups, 4).permute(0, 2, 1, 3, 4).reshape(pages * bs, H, groups, 4)
+    packed = packed[:tokens].reshape(B, S, H, groups, 4).contiguous().view(torch.uint32)
+    stats = cache[:, code_words : code_words + stat_words].reshape(pages, H, bs, groups).permute(0, 2, 1, 3)
+    stats = stats.reshape(pages * bs, H, groups)[:tokens].reshape(B, S, H, groups).contiguous()
+    halves = stats.view(stat_dtype).reshape(B, S, H, groups, 2)  # low half: scale, high half: minimum
+    return packed, halves[..., 1].contiguous(), halves[..., 0].contiguous()
+
+
+def quantize_k(
+    x: torch.Tensor,
+    num_bits: int,
+    group_size: int,
+    q_points: Optional[torch.Tensor] = None,
+    thresholds: Optional[torch.Tensor] = None,
+    pack_axis_first: bool = False,
+    stat_dtype: Optional[torch.dtype] = None,
+) -> PackedK:
+    """Quantise K in ``(B, S, H, D)`` layout, grouping along D per token (reference :439-486),
+    on the GPU; codes and statistics are bit-identical to the reference function."""
+    if pack_axis_first:
+        raise TypeError("pack_axis_first was removed; K is per-token")
+    packed, mn, scale = _quantize_rows(x, num_bits, group_size, q_points, thresholds, stat_dtype)
+    return PackedK(codes=unpack_codes(packed, num_bits, group_size), packed=packed, mn=mn, scale=scale,
+                   bits=num_bits, group_size=group_size, pack_token_last=False)
+
+
+def quantize_v(
+    x: torch.Tensor,
+    num_bits: int,
+    group_size: int,
+    q_points: Optional[torch.Tensor] = None,
+    thresholds: Optional[torch.Tensor] = None,
+    pack_token_last: bool = False,
+    stat_dtype: Optional[torch.dtype] = None,
+) -> PackedV:
+    """Quantise V in ``(B, S, H, D)`` layout, grouping along D (reference :525-584)."""
+    packed, mn, scale = _quantize_rows(x, num_bits, group_size, q_points, thresholds, stat_dtype)
+    codes = unpack_codes(packed, num_bits, group_size)
+    if pack_token_last:
+        packed = packed.permute(0, 2, 3, 4, 1).contiguous()
+        mn = mn.permute(0, 2, 3, 1).contiguous()
+        scale = scale.permute(0, 2, 3, 1).contiguous()
+    return PackedV(codes=codes, packed=packed, mn=mn, scale=scale, bits=num_bits, group_size=group_size,
+                   pack_token_last=pack_token_last)
+
+
+def _dequantize_rows(packed, q_points) -> torch.Tensor:
+    """Shared body of dequantize_k / dequantize_v (reference :499-517, :596-616): the packed
+    words and statistics are laid into a private page pool and reconstructed by the read-back
+    kernel - ``level * scale + min`` in float32 as two rounded operations, then one rounding to
+    the dtype of the statistics."""
+    _validate_real_quant_params(packed.bits, packed.group_size)
+    words, mn, scale = packed.packed, packed.mn, packed.scale
+    if packed.pack_token_last:
+        words = words.permute(0, 4, 1, 2, 3)
+        mn = mn.permute(0, 3, 1, 2)
+        scale = scale.permute(0, 3, 1, 2)
+    if not mn.is_cuda:
+        raise RuntimeError("dequantize_k / dequantize_v run on the sm_100a read-back kernel: CUDA tensors only")
+    B, S, H, groups, _ = (int(n) for n in words.shape)
+    if groups * packed.group_size != _HEAD_DIM:
+        raise RuntimeError(f"the sm_100a read-back kernel handles head_dim {_HEAD_DIM}")
+    tokens, bs = B * S, _SCRATCH_BLOCK
+    out = torch.empty((tokens, H, _HEAD_DIM), dtype=mn.dtype, device=mn.device)
+    if tokens == 0:
+        return out.reshape(B, S, H, _HEAD_DIM)
+    pages = (tokens + bs - 1) // bs
+    layout = PagedLayout.build_hnd(bs, H, _HEAD_DIM, 4, packed.group_size, packed.group_size)
+    cache = torch.zeros((pages, layout.block_i32), dtype=torch.int32, device=mn.device)
+    code_words, stat_words = H * bs * 16, H * bs * groups
+    padded = torch.zeros((pages * bs, H, groups, 4), dtype=torch.int32, device=mn.device)
+    padded[:tokens] = words.reshape(tokens, H, groups, 4).view(torch.int32)
+    cache[:, :code_words] = padded.reshape(pages, bs, H, groups, 4).permute(0, 2, 1, 3, 4).reshape(pages, code_words)
+    halves = torch.zeros((pages * bs, H, groups, 2), dtype=mn.dtype, device=mn.device)
+    halves[:tokens, ..., 0] = scale.reshape(tokens, H, groups)
+    halves[:tokens, ..., 1] = mn.reshape(tokens, H, groups)
+    stat_i32 = halves.view(torch.int32).reshape(pages, bs, H, groups)
+    cache[:, code_words : code_words + stat_words] = stat_i32.permute(0, 2, 1, 3).reshape(pages, stat_words)
+    table = torch.arange(pages, dtype=torch.int32, device=mn.device).reshape(1, pages)
+    lens = torch.tensor([tokens], dtype=torch.int32, device=mn.device)
+    starts = torch.tensor([0, tokens], dtype=torch.int32, device=mn.device)
+    unused_v = torch.empty_like(out)
+    dequantize_paged_kv_to_dense(cache, layout, table, lens, starts, out, unused_v, max_seq_len=tokens,
+                                 q_points_k=q_points, q_points_v=q_points, stat_dtype=mn.dtype)
+    return out.reshape(B, S, H, _HEAD_DIM)
+
+
+def dequantize_k(packed: PackedK, q_points: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Reconstructed K ``(B, S, H, D)`` in the dtype of the packed statistics (reference :489-517)."""
+    return _dequantize_rows(packed, q_points)
+
+
+def dequantize_v(packed: PackedV, q_points: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Reconstructed V ``(B, S, H, D)`` in the dtype of the packed statistics (reference :587-616)."""
+    return _dequantize_rows(packed, q_points)

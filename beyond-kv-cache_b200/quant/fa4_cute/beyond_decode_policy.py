@@ -1,26 +1,32 @@
-"""Launch policy of the B200 packed decode kernel (pure Python, no device access).
+"""Launch policy of the split-grid form of the B200 packed decode (pure Python, no device access).
 
-Mirror of the reference policy module ``quant/fa4_cute/beyond_decode_policy.py``:
-the same function names and the same ``DecodeLaunchPlan`` fields, so the launcher
-and its callers do not change.  The numbers are not the reference's B300 look-up
-tables: the B200 kernel keeps one persistent-size CTA per SM that owns a *run* of
-16-token tiles, so its only shape-dependent choice is the split-KV count, which is
-taken from a resident-wave cost model of that kernel (reference model:
-``modeled_splits``, ``quant/fa4_cute/beyond_decode_policy.py:165-201``).
+Mirror of the reference policy module ``quant/fa4_cute/beyond_decode_policy.py``: the same
+``DecodeLaunchPlan`` fields and the entry points the launcher calls, so the launcher and its
+callers do not change.  The numbers are not the reference's B300 look-up tables.  On B200 the
+production kernel is persistent and has no split count at all; a plan is only drawn up for the
+general split grid (``bkv_decode_sm100``: one small CTA per (split, kv head, request)), whose one
+shape-dependent choice is the split-KV count.  It comes from a resident-wave cost model of that
+kernel (the reference's counterpart is ``modeled_splits``, :165-201).  The reference's other
+choices - reducer variant, staging depths, cluster reduction, grid order, direct shared-memory
+stores (:204-334) - have no counterpart in this kernel and are recorded in the plan as the
+constants below.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
 
-TILE_TOKENS = 16  # tokens one warp consumes per step of the sm_100a kernel
+TILE_TOKENS = 16  # tokens per step of the cost model
 MAX_SPLITS = 32  # same cap as the reference launcher (runtime.py:217-218)
+REDUCTION_KIND = "lse_combine"  # the one log-sum-exp combine kernel
+KV_STAGE_CAP = 1  # the split grid reads pages with plain loads: nothing is staged
+CVT_STAGE_CAP = 1  # dequantisation happens in registers
 
-# Cost-model constants, in units of "one 16-token tile processed by one CTA".
-_CTA_FIXED_TILES = 40.0  # table build + prologue + epilogue of one CTA
-_COMBINE_BASE_TILES = 16.0  # extra launch + partial round trip when splits > 1
+_RESIDENT_CTAS_PER_SM = 12  # 128-thread CTAs of the split grid that share an SM
+_CTA_FIXED_STEPS = 6.0  # prologue + warp merge + epilogue of one CTA, in 16-token steps
+_COMBINE_BASE_STEPS = 24.0  # extra launch + partial round trip when splits > 1
 _COMBINE_PER_SPLIT = 0.02  # per (request, split) reducer work
-_REDUCTION_KINDS = ("lse_combine", "parallel", "cta4", "warp_parallel", "warp_parallel2")
+_REFERENCE_REDUCERS = ("parallel", "cta4", "warp_parallel", "warp_parallel2")
 
 
 @dataclass(frozen=True)
@@ -62,95 +68,54 @@ def modeled_splits(
 ) -> int:
     """Split-KV count that minimises ``waves * (pages_per_split + fixed) + reducer``.
 
-    One CTA is resident per SM, so ``waves = ceil(batch * heads_kv * splits /
-    sm_count)``.  More splits shorten each CTA and smooth the last wave, but every
-    CTA pays a fixed cost and ``splits > 1`` adds the combine launch.  ``tiles``
-    counts pages of ``page_size`` tokens (``page_size / 16`` kernel steps each)."""
+    ``waves = ceil(batch * heads_kv * splits / (sm_count * resident CTAs))``.  More splits
+    shorten each CTA and smooth the last wave, but every CTA pays a fixed cost and
+    ``splits > 1`` adds the combine launch.  ``tiles`` counts pages of ``page_size`` tokens
+    (``page_size / 16`` steps each).  Never more than ``tiles`` or ``max_splits``."""
     _require_positive(
         tiles=tiles, batch=batch, heads_kv=heads_kv, sm_count=sm_count, max_splits=max_splits, page_size=page_size
     )
     tasks = int(batch) * int(heads_kv)
+    slots = int(sm_count) * _RESIDENT_CTAS_PER_SM
     steps_per_page = max(1.0, int(page_size) / TILE_TOKENS)
 
     def cost(splits: int) -> tuple[float, int]:
-        waves = (tasks * splits + sm_count - 1) // sm_count
-        per_cta = ((tiles + splits - 1) // splits) * steps_per_page + _CTA_FIXED_TILES
+        waves = (tasks * splits + slots - 1) // slots
+        per_cta = ((int(tiles) + splits - 1) // splits) * steps_per_page + _CTA_FIXED_STEPS
         total = waves * per_cta
         if splits > 1:
-            total += _COMBINE_BASE_TILES + _COMBINE_PER_SPLIT * batch * splits
-        return total, splits
+            total += _COMBINE_BASE_STEPS + _COMBINE_PER_SPLIT * int(batch) * splits
+        return total, splits  # ties go to the smaller count
 
     return min(range(1, min(int(max_splits), int(tiles)) + 1), key=cost)
 
 
-def select_reduction_kind(*, batch: int, splits: int, pages_per_split: int | None = None) -> str:
-    """The B200 build has a single log-sum-exp combine kernel; the reference's
-    three reducer variants (:227-251) collapse into it."""
-    _require_positive(batch=batch, splits=splits)
-    if pages_per_split is not None:
-        _require_positive(pages_per_split=pages_per_split)
-    return "lse_combine"
-
-
 def normalize_reduction_kind(kind: str) -> str:
-    """Accept the reference's reducer names as aliases of the single combine kernel."""
+    """Accept ``auto`` and the reference's reducer names (``BEYOND_SM103_REDUCTION_KIND``,
+    :227-251) as aliases of the single combine kernel; anything else is an error."""
     kind = str(kind).strip().lower()
-    if kind == "auto":
-        return "lse_combine"
-    if kind not in _REDUCTION_KINDS:
+    if kind != "auto" and kind != REDUCTION_KIND and kind not in _REFERENCE_REDUCERS:
         raise ValueError(
             "BEYOND_SM103_REDUCTION_KIND must be auto, parallel, cta4, warp_parallel, or warp_parallel2"
         )
-    return "lse_combine"
-
-
-def packed_kv_stage_cap(*, pages_per_split: int) -> int:
-    """Depth of the per-warp page ring (tiles in flight per warp)."""
-    if int(pages_per_split) <= 0:
-        raise ValueError("packed-KV stage input must be positive: pages_per_split")
-    return 4
-
-
-def conversion_stage_cap(*, splits: int, pages_per_split: int, model_dtype: str | None = None) -> int:
-    """Dequantisation happens in registers, so there is no conversion staging."""
-    _require_positive(splits=splits, pages_per_split=pages_per_split)
-    if model_dtype not in (None, "fp16", "bf16"):
-        raise ValueError(f"unsupported model_dtype: {model_dtype}")
-    return 1
-
-
-def select_cluster_splits(*, tiles: int, batch: int, heads_kv: int) -> int:
-    """No thread-block-cluster reduction in this build: always 0."""
-    _require_positive(tiles=tiles, batch=batch, heads_kv=heads_kv)
-    return 0
-
-
-def select_direct_smem_store(*, batch: int, heads_kv: int, splits: int, pages_per_split: int) -> bool:
-    _require_positive(batch=batch, heads_kv=heads_kv, splits=splits, pages_per_split=pages_per_split)
-    return False
-
-
-def select_task_major_grid(*, batch: int, splits: int, pages_per_split: int) -> bool:
-    _require_positive(batch=batch, splits=splits, pages_per_split=pages_per_split)
-    return False
+    return REDUCTION_KIND
 
 
 def select_decode_launch_plan(
     *, tiles: int, batch: int, heads_kv: int, sm_count: int, model_dtype: str, page_size: int = TILE_TOKENS
 ) -> DecodeLaunchPlan:
-    """Plan for one bucket; ``tiles`` is the number of *pages* of the bucket
+    """Plan for one bucket of the split grid; ``tiles`` is the number of *pages* of the bucket
     (``max_seq_len // page_size``), as in the reference (:337-433)."""
     _require_positive(tiles=tiles, batch=batch, heads_kv=heads_kv, sm_count=sm_count)
     if model_dtype not in {"fp16", "bf16"}:
         raise ValueError(f"unsupported model_dtype: {model_dtype}")
     splits = modeled_splits(tiles=tiles, batch=batch, heads_kv=heads_kv, sm_count=sm_count, page_size=page_size)
-    pages = scheduled_pages_per_split(tiles=tiles, splits=splits)
     return DecodeLaunchPlan(
         splits=splits,
-        pages_per_split=pages,
-        reduction_kind=select_reduction_kind(batch=batch, splits=splits, pages_per_split=pages),
-        kv_stage_cap=packed_kv_stage_cap(pages_per_split=pages),
-        cvt_stage_cap=conversion_stage_cap(splits=splits, pages_per_split=pages, model_dtype=model_dtype),
+        pages_per_split=scheduled_pages_per_split(tiles=tiles, splits=splits),
+        reduction_kind=REDUCTION_KIND,
+        kv_stage_cap=KV_STAGE_CAP,
+        cvt_stage_cap=CVT_STAGE_CAP,
         cluster_reduction=False,
         task_major_grid=False,
         direct_smem_store=False,

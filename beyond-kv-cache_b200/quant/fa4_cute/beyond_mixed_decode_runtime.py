@@ -5,8 +5,9 @@ Mirror of the reference launcher ``quant/fa4_cute/beyond_mixed_decode_runtime.py
 ``allocate_runtime_workspace``, ``run_nonuniform_decode`` and
 ``clear_compiled_runtime_cache`` keep their names, arguments and error types.
 Instead of JIT-compiling a CuTe DSL kernel per launch bucket, every call goes to the
-pre-built sm_100a library through the C ABI (``bkv_decode_sm100``): nothing is
-compiled or allocated at launch, so a launch is capturable without pre-warming.
+pre-built sm_100a library through the C ABI (``bkv_decode_stream_sm100``, or
+``bkv_decode_sm100`` for an explicit split count): nothing is compiled or allocated at
+launch, so a launch is capturable without pre-warming.
 
 Differences from the reference contract, all additive:
 
@@ -33,9 +34,9 @@ import torch
 from ... import _lib
 from ..beyond_cute import CODE_LAYOUT_HND_TOKEN_WORD, PagedLayout
 from .beyond_decode_policy import (
-    conversion_stage_cap,
+    CVT_STAGE_CAP,
+    KV_STAGE_CAP,
     normalize_reduction_kind,
-    packed_kv_stage_cap,
     scheduled_pages_per_split,
     select_decode_launch_plan,
 )
@@ -51,7 +52,9 @@ _SM_COUNT: dict[int, int] = {}
 @dataclass(frozen=True)
 class DecodeRuntimeSpec:
     """Frozen description of one launch bucket (fields of the reference spec,
-    ``beyond_mixed_decode_runtime.py:43-73``); hashable, used as a workspace key."""
+    ``beyond_mixed_decode_runtime.py:43-73``); hashable, used as a workspace key.
+    ``persistent`` (additive) says that the bucket runs under the persistent schedule, which
+    has no split count (``num_splits`` is then 1 and no split workspace is needed)."""
 
     device_index: int
     model_dtype: str
@@ -73,26 +76,74 @@ class DecodeRuntimeSpec:
     task_major_grid: bool
     direct_smem_store: bool
     wait_for_pdl_writer: bool
+    persistent: bool = False
 
     @property
     def pages_per_split(self) -> int:
         return scheduled_pages_per_split(tiles=self.max_seq_len // self.page_size, splits=self.num_splits)
 
 
+_DTYPE_NAMES = {torch.float16: "fp16", torch.bfloat16: "bf16"}
+_DTYPES = {name: dtype for dtype, name in _DTYPE_NAMES.items()}
+
+
 def _dtype_name(dtype: torch.dtype) -> str:
-    if dtype == torch.float16:
-        return "fp16"
-    if dtype == torch.bfloat16:
-        return "bf16"
-    raise TypeError(f"expected fp16 or bf16, got {dtype}")
+    try:
+        return _DTYPE_NAMES[dtype]
+    except KeyError:
+        raise TypeError(f"expected fp16 or bf16, got {dtype}") from None
 
 
 def _torch_dtype(name: str) -> torch.dtype:
-    if name == "fp16":
-        return torch.float16
-    if name == "bf16":
-        return torch.bfloat16
-    raise ValueError(f"unsupported dtype name {name!r}")
+    try:
+        return _DTYPES[name]
+    except KeyError:
+        raise ValueError(f"unsupported dtype name {name!r}") from None
+
+
+def _first_failure(checks):
+    """``checks`` yields (ok, message) pairs in contract order; raise ValueError for the first
+    pair that is not ok.  The messages are part of the interface (callers match fragments)."""
+    for ok, message in checks:
+        if not ok:
+            raise ValueError(message)
+
+
+class _ByteTables:
+    """The expanded look-up tables of one layer's decode tables (128 KiB per kv head), built
+    once by :func:`prepare_runtime_qpoints` and handed to every launch of that layer."""
+
+    __slots__ = ("tables", "k_version", "v_version", "v_ref")
+
+    def __init__(self, tables, k, v):
+        self.tables, self.k_version, self.v_version, self.v_ref = tables, k._version, v._version, v
+
+
+def _build_byte_tables(k_lane_major: torch.Tensor, v_code_major: torch.Tensor) -> torch.Tensor:
+    heads_kv = int(k_lane_major.shape[0])
+    with torch.cuda.device(k_lane_major.device):
+        nbytes = int(_lib.load().bkv_decode_tables_bytes(heads_kv))
+        tables = torch.empty((nbytes,), dtype=torch.uint8, device=k_lane_major.device)
+        _lib.call(
+            "bkv_decode_tables_sm100", k_lane_major.data_ptr(), v_code_major.data_ptr(),
+            _lib.dtype_code(k_lane_major.dtype), heads_kv, _lib.FLAG_KLEVELS_LANE_MAJOR,
+            tables.data_ptr(), nbytes, _lib.current_stream(k_lane_major.device),
+        )
+    return tables
+
+
+def _byte_tables_of(k_lane_major: torch.Tensor, v_code_major: torch.Tensor) -> Optional[torch.Tensor]:
+    """Tables attached by :func:`prepare_runtime_qpoints`, if they still describe these two
+    tensors (same objects, not modified since); None makes the kernel build its own."""
+    held = getattr(k_lane_major, "_bkv_byte_tables", None)
+    if (
+        held is None
+        or held.v_ref is not v_code_major
+        or held.k_version != k_lane_major._version
+        or held.v_version != v_code_major._version
+    ):
+        return None
+    return held.tables
 
 
 def prepare_runtime_qpoints(
@@ -102,27 +153,29 @@ def prepare_runtime_qpoints(
     heads_kv: int,
     storage_dtype: torch.dtype = torch.float16,
 ) -> tuple[torch.Tensor, torch.Tensor]:
-    """Decode-side level tables: K as ``(Hkv, 16, 4)`` (level-major, group minor),
-    V as ``(Hkv, 4, 16)``, both 16-bit — the shapes of the reference launcher
-    (``beyond_mixed_decode_runtime.py:92-134``)."""
-    if storage_dtype not in (torch.float16, torch.bfloat16):
+    """Decode-side level tables, once per layer: K as ``(Hkv, 16, 4)`` (level-major, group
+    minor), V as ``(Hkv, 4, 16)``, both 16-bit — the shapes of the reference launcher
+    (``beyond_mixed_decode_runtime.py:92-134``).  On a CUDA device the byte-indexed look-up
+    tables of the decode kernel are expanded here too and travel with the K tensor."""
+    if storage_dtype not in _DTYPE_NAMES:
         raise TypeError("runtime qpoints must use 16-bit fp16 or bf16 storage")
     groups = _HEAD_DIM // _GROUP_SIZE
     expected = int(heads_kv) * groups
 
     def grouped(table: torch.Tensor, label: str) -> torch.Tensor:
-        if table.numel() != expected * 16:
-            raise ValueError(
-                f"{label} qpoints require {expected} independent 16-point tables, got {table.numel()} values"
-            )
-        if table.ndim == 2 and tuple(table.shape) != (expected, 16):
-            raise ValueError(f"{label} qpoints must have shape ({expected}, 16), got {tuple(table.shape)}")
-        if table.ndim not in (2, 3):
-            raise ValueError(f"{label} qpoints must be rank 2 or 3")
+        _first_failure((
+            (table.numel() == expected * 16,
+             f"{label} qpoints require {expected} independent 16-point tables, got {table.numel()} values"),
+            (table.ndim != 2 or tuple(table.shape) == (expected, 16),
+             f"{label} qpoints must have shape ({expected}, 16), got {tuple(table.shape)}"),
+            (table.ndim in (2, 3), f"{label} qpoints must be rank 2 or 3"),
+        ))
         return table.reshape(int(heads_kv), groups, 16)
 
     k_lane_major = grouped(q_points_k, "K").permute(0, 2, 1).to(dtype=storage_dtype).contiguous()
     v_code_major = grouped(q_points_v, "V").to(dtype=storage_dtype).contiguous()
+    if k_lane_major.is_cuda and v_code_major.is_cuda and not torch.cuda.is_current_stream_capturing():
+        k_lane_major._bkv_byte_tables = _ByteTables(_build_byte_tables(k_lane_major, v_code_major), k_lane_major, v_code_major)
     return k_lane_major, v_code_major
 
 
@@ -132,6 +185,13 @@ def _sm_count(device: torch.device) -> int:
         if index not in _SM_COUNT:
             _SM_COUNT[index] = torch.cuda.get_device_properties(index).multi_processor_count
         return _SM_COUNT[index]
+
+
+def persistent_schedule_supported(*, batch_size: int, physical_pages: int, heads_q: int, heads_kv: int) -> bool:
+    """Limits of ``bkv_decode_stream_sm100``: at most 16384 requests per launch, page ids of
+    26 bits and 2^20 (kv head x query-head quad, request) pairs; larger buckets use the split grid."""
+    quads = (heads_q // heads_kv + 3) // 4
+    return batch_size <= 16384 and physical_pages <= (1 << 26) and heads_kv * quads * batch_size <= (1 << 20)
 
 
 def make_runtime_spec(
@@ -146,7 +206,11 @@ def make_runtime_spec(
     qpoint_dtype: torch.dtype = torch.float16,
     wait_for_pdl_writer: bool = False,
 ) -> DecodeRuntimeSpec:
-    """Validate a launch bucket and freeze its launch plan (reference :137-302)."""
+    """Validate a launch bucket and freeze its launch plan (reference :137-302).
+
+    ``num_splits <= 0`` leaves the schedule to the library: the persistent kernel (no split
+    count) when the bucket fits its limits, else the split grid with the count the launch
+    policy picks.  ``num_splits >= 1`` asks for the split grid with exactly that count."""
     if not q.is_cuda or not cache.is_cuda or not block_table.is_cuda:
         raise ValueError("q, packed cache, and block_table must be CUDA tensors")
     if torch.cuda.get_device_capability(q.device)[0] != 10:
@@ -154,61 +218,47 @@ def make_runtime_spec(
     model_dtype = _dtype_name(q.dtype)
     qpoint_dtype_name = _dtype_name(qpoint_dtype)
     page_size = int(layout.block_size)
-    if page_size not in SUPPORTED_PAGE_SIZES:
-        raise ValueError("packed cache block_size must be 16, 32, 64 or 128")
-    if layout.code_layout != CODE_LAYOUT_HND_TOKEN_WORD or layout.abi_version != 2:
-        raise ValueError("packed cache must use HND token-major ABI v2")
-    if not layout.v_stats_group_major:
-        raise ValueError("packed cache V statistics must retain PV group-major order")
-    if (
-        layout.bits != 4
-        or layout.k_group_size != _GROUP_SIZE
-        or layout.v_group_size != _GROUP_SIZE
-        or layout.head_dim != _HEAD_DIM
-    ):
-        raise ValueError("launcher requires independent K/V Int4-G32-D128 cache")
-    if cache.dtype != torch.int32 or cache.ndim != 2 or not cache.is_contiguous():
-        raise ValueError("cache must be contiguous (physical_pages, block_i32) int32")
-    if int(cache.shape[1]) != int(layout.block_i32):
-        raise ValueError("cache row stride does not match PagedLayout.block_i32")
-    if block_table.dtype != torch.int32 or block_table.ndim != 2:
-        raise ValueError("block_table must be a rank-2 int32 CUDA tensor")
-    if block_table.stride(1) != 1:
-        raise ValueError("block_table must be contiguous within each request row")
-    if max_seq_len <= 0 or max_seq_len % page_size:
-        raise ValueError(f"max_seq_len must be a positive multiple of page_size={page_size}")
+    heads_kv = int(layout.num_kv_heads)
+    _first_failure((
+        (page_size in SUPPORTED_PAGE_SIZES, "packed cache block_size must be 16, 32, 64 or 128"),
+        (layout.code_layout == CODE_LAYOUT_HND_TOKEN_WORD and layout.abi_version == 2,
+         "packed cache must use HND token-major ABI v2"),
+        (layout.v_stats_group_major, "packed cache V statistics must retain PV group-major order"),
+        (layout.bits == 4 and layout.k_group_size == _GROUP_SIZE and layout.v_group_size == _GROUP_SIZE
+         and layout.head_dim == _HEAD_DIM, "launcher requires independent K/V Int4-G32-D128 cache"),
+        (cache.dtype == torch.int32 and cache.ndim == 2 and cache.is_contiguous(),
+         "cache must be contiguous (physical_pages, block_i32) int32"),
+        (cache.ndim == 2 and int(cache.shape[1]) == int(layout.block_i32),
+         "cache row stride does not match PagedLayout.block_i32"),
+        (block_table.dtype == torch.int32 and block_table.ndim == 2, "block_table must be a rank-2 int32 CUDA tensor"),
+        (block_table.ndim == 2 and block_table.stride(1) == 1, "block_table must be contiguous within each request row"),
+        (max_seq_len > 0 and max_seq_len % page_size == 0,
+         f"max_seq_len must be a positive multiple of page_size={page_size}"),
+        (block_table.ndim == 2 and max_seq_len // page_size <= int(block_table.shape[1]),
+         "launch bucket exceeds the block-table capacity"),
+        (q.ndim == 3 and tuple(q.shape[1:]) == (int(heads_q), _HEAD_DIM), "q must have shape (B, Hq, D128)"),
+        (q.ndim == 3 and int(q.shape[0]) > 0, "q decode batch must be non-empty"),
+        (q.ndim == 3 and int(q.stride(2)) == 1 and int(q.stride(1)) == _HEAD_DIM,
+         "q must be contiguous within each attention head"),
+        (q.ndim == 3 and int(q.stride(0)) >= int(heads_q) * _HEAD_DIM, "q batch stride overlaps adjacent decode rows"),
+        (int(heads_q) % heads_kv == 0, "heads_q must be divisible by heads_kv"),
+        (int(heads_q) // heads_kv in (1, 2, 4, 8), "heads_q / heads_kv must be 1, 2, 4 or 8"),
+    ))
     logical_pages = max_seq_len // page_size
-    if logical_pages > int(block_table.shape[1]):
-        raise ValueError("launch bucket exceeds the block-table capacity")
-    if q.ndim != 3 or tuple(q.shape[1:]) != (int(heads_q), _HEAD_DIM):
-        raise ValueError("q must have shape (B, Hq, D128)")
     batch_size = int(q.shape[0])
-    if batch_size <= 0:
-        raise ValueError("q decode batch must be non-empty")
-    if int(q.stride(2)) != 1 or int(q.stride(1)) != _HEAD_DIM:
-        raise ValueError("q must be contiguous within each attention head")
-    q_batch_stride = int(q.stride(0))
-    if q_batch_stride < int(heads_q) * _HEAD_DIM:
-        raise ValueError("q batch stride overlaps adjacent decode rows")
-    if int(heads_q) % int(layout.num_kv_heads):
-        raise ValueError("heads_q must be divisible by heads_kv")
-    if int(heads_q) // int(layout.num_kv_heads) not in (1, 2, 4, 8):
-        raise ValueError("heads_q / heads_kv must be 1, 2, 4 or 8")
-
+    persistent = num_splits <= 0 and persistent_schedule_supported(
+        batch_size=batch_size, physical_pages=int(cache.shape[0]), heads_q=int(heads_q), heads_kv=heads_kv)
     plan = None
-    if num_splits <= 0:
+    if persistent:
+        num_splits = 1
+    elif num_splits <= 0:
         plan = select_decode_launch_plan(
-            tiles=logical_pages,
-            batch=batch_size,
-            heads_kv=int(layout.num_kv_heads),
-            sm_count=_sm_count(q.device),
-            model_dtype=model_dtype,
-            page_size=page_size,
+            tiles=logical_pages, batch=batch_size, heads_kv=heads_kv, sm_count=_sm_count(q.device),
+            model_dtype=model_dtype, page_size=page_size,
         )
         num_splits = plan.splits
     if not 1 <= int(num_splits) <= 32:
         raise ValueError("num_splits must be in [1, 32]")
-    pages_per_split = scheduled_pages_per_split(tiles=logical_pages, splits=int(num_splits))
     reduction_kind = normalize_reduction_kind(
         os.environ.get("BEYOND_SM100_REDUCTION_KIND", os.environ.get("BEYOND_SM103_REDUCTION_KIND", "auto"))
     )
@@ -218,89 +268,75 @@ def make_runtime_spec(
         qpoint_dtype=qpoint_dtype_name,
         batch_size=batch_size,
         heads_q=int(heads_q),
-        heads_kv=int(layout.num_kv_heads),
+        heads_kv=heads_kv,
         max_seq_len=int(max_seq_len),
         page_size=page_size,
         num_splits=int(num_splits),
         physical_pages=int(cache.shape[0]),
         page_table_stride=int(block_table.stride(0)),
         packed_page_stride_i32=int(layout.block_i32),
-        q_batch_stride=q_batch_stride,
-        kv_stage_cap=plan.kv_stage_cap if plan is not None else packed_kv_stage_cap(pages_per_split=pages_per_split),
-        cvt_stage_cap=plan.cvt_stage_cap
-        if plan is not None
-        else conversion_stage_cap(splits=int(num_splits), pages_per_split=pages_per_split, model_dtype=model_dtype),
+        q_batch_stride=int(q.stride(0)),
+        kv_stage_cap=KV_STAGE_CAP,
+        cvt_stage_cap=CVT_STAGE_CAP,
         reduction_kind=reduction_kind,
         cluster_reduction=False,
         task_major_grid=False,
         direct_smem_store=False,
         wait_for_pdl_writer=bool(wait_for_pdl_writer),
+        persistent=persistent,
     )
 
 
 def allocate_runtime_workspace(spec: DecodeRuntimeSpec, *, device: torch.device) -> dict[str, torch.Tensor]:
-    """Allocate the split workspace once, before any CUDA-graph capture
-    (reference :305-324).  All three tensors are float32."""
-    partial_shape = (spec.num_splits, spec.batch_size, spec.heads_q, 1, _HEAD_DIM)
+    """Allocate the workspace of a bucket once, before any CUDA-graph capture (reference
+    :305-324).  A split-grid bucket gets the three float32 partial tensors; a persistent
+    bucket gets the schedule's scratch under ``"stream"`` (its size depends on the device
+    only) and empty partial tensors, since nothing would read them."""
+    splits = 0 if spec.persistent else spec.num_splits
+    partial_shape = (splits, spec.batch_size, spec.heads_q, 1, _HEAD_DIM)
     ws = {
         "o_partial": torch.empty(partial_shape, dtype=torch.float32, device=device),
         "m_partial": torch.empty(partial_shape[:-1], dtype=torch.float32, device=device),
         "l_partial": torch.empty(partial_shape[:-1], dtype=torch.float32, device=device),
     }
-    if stream_schedule_supported(spec):
-        # scratch of the persistent schedule (partials of requests cut between workers);
-        # its size depends on the device only
-        with torch.cuda.device(device):
-            nbytes = int(_lib.load().bkv_decode_stream_workspace_bytes())
-        ws["stream"] = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    if spec.persistent:
+        ws["stream"] = _lib.stream_workspace(torch.device(device))
     return ws
-
-
-def stream_schedule_supported(spec: DecodeRuntimeSpec) -> bool:
-    """The persistent schedule (``bkv_decode_stream_sm100``) plans at most 16384 requests
-    per launch and packs page ids into 26 bits; larger buckets use the split grid."""
-    return spec.batch_size <= 16384 and spec.physical_pages <= (1 << 26)
 
 
 def _validate_launch_tensors(*, spec, q, out, block_table, seq_lens, k_qpoints_lane_major, v_qpoints_code_major, workspace) -> None:
     expected_shape = (spec.batch_size, spec.heads_q, _HEAD_DIM)
     expected_q = spec.batch_size * spec.heads_q * _HEAD_DIM
-    if (
-        tuple(q.shape) != expected_shape
-        or int(q.stride(2)) != 1
-        or int(q.stride(1)) != _HEAD_DIM
-        or int(q.stride(0)) != spec.q_batch_stride
-    ):
-        raise ValueError("q shape or fused-QKV batch stride changed after compilation")
-    if out.dtype != q.dtype or not out.is_contiguous() or out.numel() != expected_q:
-        raise ValueError("out must match the contiguous dense q bucket")
-    if block_table.dtype != torch.int32 or block_table.stride(1) != 1:
-        raise ValueError("block_table must retain the compiled int32 row layout")
-    if int(block_table.stride(0)) != spec.page_table_stride:
-        raise ValueError("block_table row stride changed after compilation")
-    if seq_lens.dtype != torch.int32 or not seq_lens.is_contiguous():
-        raise ValueError("seq_lens must be contiguous int32")
-    if seq_lens.numel() < spec.batch_size:
-        raise ValueError("seq_lens is shorter than the decode batch")
     groups = _HEAD_DIM // _GROUP_SIZE
-    expected_k = (spec.heads_kv, 16, groups)
-    expected_v = (spec.heads_kv, groups, 16)
-    if tuple(k_qpoints_lane_major.shape) != expected_k:
-        raise ValueError(f"K runtime qpoints must have shape {expected_k}")
-    if tuple(v_qpoints_code_major.shape) != expected_v:
-        raise ValueError(f"V runtime qpoints must have shape {expected_v}")
-    if (
-        not k_qpoints_lane_major.is_contiguous()
-        or not v_qpoints_code_major.is_contiguous()
-        or k_qpoints_lane_major.dtype != v_qpoints_code_major.dtype
-        or _dtype_name(k_qpoints_lane_major.dtype) != spec.qpoint_dtype
-    ):
-        raise ValueError("K/V qpoints must be contiguous and share the compiled 16-bit dtype")
-    if spec.num_splits > 1:
+    expected_k, expected_v = (spec.heads_kv, 16, groups), (spec.heads_kv, groups, 16)
+    _first_failure((
+        (tuple(q.shape) == expected_shape and int(q.stride(2)) == 1 and int(q.stride(1)) == _HEAD_DIM
+         and int(q.stride(0)) == spec.q_batch_stride, "q shape or fused-QKV batch stride changed after compilation"),
+        (out.dtype == q.dtype and out.is_contiguous() and out.numel() == expected_q,
+         "out must match the contiguous dense q bucket"),
+        (block_table.dtype == torch.int32 and block_table.stride(1) == 1,
+         "block_table must retain the compiled int32 row layout"),
+        (int(block_table.stride(0)) == spec.page_table_stride, "block_table row stride changed after compilation"),
+        (seq_lens.dtype == torch.int32 and seq_lens.is_contiguous(), "seq_lens must be contiguous int32"),
+        (seq_lens.numel() >= spec.batch_size, "seq_lens is shorter than the decode batch"),
+        (tuple(k_qpoints_lane_major.shape) == expected_k, f"K runtime qpoints must have shape {expected_k}"),
+        (tuple(v_qpoints_code_major.shape) == expected_v, f"V runtime qpoints must have shape {expected_v}"),
+        (k_qpoints_lane_major.is_contiguous() and v_qpoints_code_major.is_contiguous()
+         and k_qpoints_lane_major.dtype == v_qpoints_code_major.dtype
+         and _DTYPE_NAMES.get(k_qpoints_lane_major.dtype) == spec.qpoint_dtype,
+         "K/V qpoints must be contiguous and share the compiled 16-bit dtype"),
+    ))
+    if spec.persistent:
+        scratch = workspace.get("stream")
+        if scratch is None or scratch.dtype != torch.uint8 or not scratch.is_contiguous():
+            raise ValueError("stream workspace is missing: allocate it with allocate_runtime_workspace")
+    elif spec.num_splits > 1:
         stats_numel = spec.num_splits * spec.batch_size * spec.heads_q
         partial = workspace.get("o_partial")
-        if partial is None or partial.dtype != torch.float32 or not partial.is_contiguous() or partial.numel() < spec.num_splits * expected_q:
-            raise ValueError("o_partial workspace is missing or undersized")
+        _first_failure((
+            (partial is not None and partial.dtype == torch.float32 and partial.is_contiguous()
+             and partial.numel() >= spec.num_splits * expected_q, "o_partial workspace is missing or undersized"),
+        ))
         for name in ("m_partial", "l_partial"):
             value = workspace.get(name)
             if value is None or value.dtype != torch.float32 or not value.is_contiguous() or value.numel() < stats_numel:
@@ -322,10 +358,12 @@ def run_nonuniform_decode(
     softmax_scale: float,
     stat_dtype: Optional[torch.dtype] = None,
     out_f32: Optional[torch.Tensor] = None,
-    variant: int = 0,
+    loader: int = 0,
 ) -> torch.Tensor:
     """Launch one dense single-token decode bucket on the current stream
-    (reference :520-612).  No allocation, no host synchronisation."""
+    (reference :520-612).  No allocation, no host synchronisation.  ``loader`` (persistent
+    buckets only) selects how tiles are brought into shared memory: 0 = 16-byte asynchronous
+    copies, 1 = tensor copies."""
     _validate_launch_tensors(
         spec=spec, q=q, out=out, block_table=block_table, seq_lens=seq_lens,
         k_qpoints_lane_major=k_qpoints_lane_major, v_qpoints_code_major=v_qpoints_code_major,
@@ -337,8 +375,7 @@ def run_nonuniform_decode(
         raise ValueError("out_f32 must be a contiguous float32 tensor of the output size")
     stat = stat_dtype if stat_dtype is not None else q.dtype
     flags = _lib.FLAG_KLEVELS_LANE_MAJOR | (_lib.FLAG_PDL_WAIT if spec.wait_for_pdl_writer else 0)
-    use_stream = (variant == 0 or variant >= 40) and "stream" in workspace and stream_schedule_supported(spec)
-    if use_stream:
+    if spec.persistent:
         scratch = workspace["stream"]
         _lib.call(
             "bkv_decode_stream_sm100",
@@ -350,12 +387,13 @@ def run_nonuniform_decode(
             _lib.dtype_code(k_qpoints_lane_major.dtype),
             out.data_ptr(), _lib.dtype_code(out.dtype), _lib.ptr(out_f32),
             scratch.data_ptr(), int(scratch.numel()),
+            _lib.ptr(_byte_tables_of(k_qpoints_lane_major, v_qpoints_code_major)),
             spec.batch_size, spec.heads_q, spec.max_seq_len,
-            float(softmax_scale), flags, int(variant), _lib.current_stream(q.device),
+            float(softmax_scale), flags, int(loader), _lib.current_stream(q.device),
         )
         return out
-    if variant >= 40:
-        raise ValueError("the persistent schedule was requested but this bucket does not support it")
+    if loader:
+        raise ValueError("the tile loader is a choice of the persistent schedule; this bucket uses the split grid")
     multi = spec.num_splits > 1
     _lib.call(
         "bkv_decode_sm100",
@@ -370,7 +408,7 @@ def run_nonuniform_decode(
         workspace["m_partial"].data_ptr() if multi else None,
         workspace["l_partial"].data_ptr() if multi else None,
         spec.num_splits, spec.batch_size, spec.heads_q, spec.max_seq_len,
-        float(softmax_scale), flags, int(variant), _lib.current_stream(q.device),
+        float(softmax_scale), flags, _lib.current_stream(q.device),
     )
     return out
 

@@ -18,7 +18,10 @@ reference, :3644-3649, :3812-3820):
 * all-prefill batch (every query covers its whole sequence): encode-on-write with
   in-place reconstruction of K/V, then causal attention over the *rounded* K/V.  The
   reference hands those to FlashAttention (a library call outside this path); here the
-  dense attention is ``torch.nn.functional.scaled_dot_product_attention`` per request.
+  dense attention is ``torch.nn.functional.scaled_dot_product_attention`` per request;
+* homogeneous chunked prefill (every request: more than one query token behind context that
+  is already cached; reference :2523-2625): encode-on-write of the chunk, read-back of every
+  request's whole context into a bounded dense view, causal attention over that view.
 """
 
 from __future__ import annotations
@@ -31,6 +34,8 @@ import torch
 from ...quant.beyond_cute import (
     CODE_LAYOUT_HND_TOKEN_WORD,
     PagedLayout,
+    classify_tables,
+    dequantize_paged_kv_to_dense,
     prepare_qpoints_and_thresholds,
     write_tokens_to_paged_cache,
 )
@@ -170,6 +175,9 @@ class BeyondPackedMetadataBuilder:
         return m
 
 
+_CHUNKED_PREFILL_WORKSPACE_MB = 1024  # bound of the dense read-back view (reference :2194-2220)
+
+
 class BeyondPackedImpl:
     """Per-layer attention implementation (reference ``BeyondPackedImpl``)."""
 
@@ -180,32 +188,36 @@ class BeyondPackedImpl:
         self.head_size = int(head_size)
         self.scale = float(scale)
         self.num_kv_heads = int(num_kv_heads if num_kv_heads is not None else num_heads)
-        self._tables = None
+        self._tables = (None, None, None, None)
+        self._device_tables: dict = {}
         self._workspaces: dict = {}
+        self._dense_workspace = None
 
     # -- quantiser tables --------------------------------------------------------------
     def set_quant_tables(self, q_points_k, thresholds_k, q_points_v, thresholds_v) -> None:
         """Per-layer tables, shared ``(16,)/(15,)`` or per-(head, group) ``(Hkv*4, 16)/(Hkv*4, 15)``
-        (what the reference resolves from its quant-config file, :2076-2172)."""
+        (what the reference resolves from its quant-config file, :2076-2172).  They are uploaded,
+        classified and expanded for the decode kernel once per device, on first use, and those
+        device tensors are kept alive here: a forward pass uploads and inspects nothing."""
         self._tables = (q_points_k, thresholds_k, q_points_v, thresholds_v)
-        self.__dict__.pop("_runtime_tables", None)
+        self._device_tables.clear()
 
-    def _resolve_tables(self, device):
-        tables = getattr(self, "_tables", None) or (None, None, None, None)
-        qk, tk = prepare_qpoints_and_thresholds(num_bits=4, device=device, q_points=tables[0], thresholds=tables[1])
-        qv, tv = prepare_qpoints_and_thresholds(num_bits=4, device=device, q_points=tables[2], thresholds=tables[3])
-        return qk, tk, qv, tv
-
-    def _runtime_qpoints(self, qk, qv):
-        cached = self.__dict__.get("_runtime_tables")
-        if cached is None or cached[0] is not qk or cached[1] is not qv:
+    def _tables_on(self, device):
+        """(q_points_k, thresholds_k, q_points_v, thresholds_v, runtime K levels, runtime V levels)."""
+        key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+        held = self._device_tables.get(key)
+        if held is None:
+            qk, tk = prepare_qpoints_and_thresholds(num_bits=4, device=device, q_points=self._tables[0], thresholds=self._tables[1])
+            qv, tv = prepare_qpoints_and_thresholds(num_bits=4, device=device, q_points=self._tables[2], thresholds=self._tables[3])
+            if qk.dtype != qv.dtype:  # the kernels take one table dtype per call
+                qk, tk, qv, tv = (t.to(torch.float32) for t in (qk, tk, qv, tv))
+            classify_tables(tk, tv)  # sorted or not: decided here, once, not on the write path
             n = self.num_kv_heads * 4
             gk = qk if qk.dim() == 2 else qk.unsqueeze(0).expand(n, 16)
             gv = qv if qv.dim() == 2 else qv.unsqueeze(0).expand(n, 16)
             rk, rv = _rt.prepare_runtime_qpoints(gk.contiguous(), gv.contiguous(), heads_kv=self.num_kv_heads)
-            cached = (qk, qv, rk, rv)
-            self._runtime_tables = cached
-        return cached[2], cached[3]
+            held = self._device_tables[key] = (qk, tk, qv, tv, rk, rv)
+        return held
 
     # -- forward -----------------------------------------------------------------------
     def forward(self, layer, query, key, value, kv_cache, attn_metadata, output=None, output_scale=None, output_block_scale=None):
@@ -241,30 +253,33 @@ class BeyondPackedImpl:
         q_lens = [int(q_starts[i + 1]) - int(q_starts[i]) for i in range(num_reqs)]
         if num_reqs == 0 or num_actual == 0:
             return output
-        qk, tk, qv, tv = self._resolve_tables(q.device)
+        tables = self._tables_on(q.device)
         slots = attn_metadata.slot_mapping[:num_actual]
         block_table = attn_metadata.block_table
 
         if all(n == 1 for n in q_lens) and num_actual == num_reqs:
             return self._decode(q, k, v, output, kv_cache, layout, block_table, attn_metadata.seq_lens, slots,
-                                seq_lens_cpu, qk, tk, qv, tv)
+                                seq_lens_cpu, tables)
         if all(n == int(s) for n, s in zip(q_lens, seq_lens_cpu)):
-            return self._prefill(q, k, v, output, kv_cache, layout, block_table, slots, q_starts, qk, tk, qv, tv)
+            return self._prefill(q, k, v, output, kv_cache, layout, block_table, slots, q_starts, tables)
+        if all(1 < n < int(s) for n, s in zip(q_lens, seq_lens_cpu)):
+            return self._chunked_prefill(q, k, v, output, kv_cache, layout, block_table, attn_metadata.seq_lens, slots,
+                                         q_starts, seq_lens_cpu, tables)
         raise NotImplementedError(
             "Beyond production attention could not represent this mixed or chunked-prefill scheduler plan."
         )
 
-    def _decode(self, q, k, v, output, cache, layout, block_table, seq_lens, slots, seq_lens_cpu, qk, tk, qv, tv):
+    def _decode(self, q, k, v, output, cache, layout, block_table, seq_lens, slots, seq_lens_cpu, tables):
+        qk, tk, qv, tv, rk, rv = tables
         batch = int(q.shape[0])
+        # Everything the attention grid reads before its programmatic wait - sequence lengths,
+        # block table, queries, its workspace - is in place BEFORE the writer is launched, so that
+        # the writer is the launch that immediately precedes the attention grid (the only launch
+        # whose output that grid may not see until it has waited).
         if slots.dtype != torch.int32 or not slots.is_contiguous():
             slots = slots.to(torch.int32).contiguous()
-        # the current token is written first and then attended like any other (:2953-2969); the
-        # writer lets the attention grid start its set-up early and that grid waits before its
-        # first cache read (BEYOND_SM103_WRITER_PDL, on by default as in the reference :2955)
-        writer_pdl = env_bool("BEYOND_SM103_WRITER_PDL", True)
-        write_tokens_to_paged_cache(cache, layout, block_table, slots[:batch], k[:batch], v[:batch], q_points_k=qk,
-                                    q_points_v=qv, thresholds_k=tk, thresholds_v=tv, signal_pdl_dependents=writer_pdl,
-                                    require_fast=True)
+        if seq_lens.dtype != torch.int32 or not seq_lens.is_contiguous():
+            seq_lens = seq_lens.to(torch.int32).contiguous()
         bs = int(layout.block_size)
         need = max(int(x) for x in seq_lens_cpu)
         capacity = int(block_table.shape[1]) * bs
@@ -272,7 +287,9 @@ class BeyondPackedImpl:
         while bucket < need:  # power-of-two launch bucket, capped by the block-table capacity (:372-393)
             bucket *= 2
         max_seq_len = min(bucket, capacity)
-        rk, rv = self._runtime_qpoints(qk, qv)
+        # the writer lets the attention grid start its set-up early and that grid waits before its
+        # first cache read (BEYOND_SM103_WRITER_PDL, on by default as in the reference :2955)
+        writer_pdl = env_bool("BEYOND_SM103_WRITER_PDL", True)
         spec = _rt.make_runtime_spec(q=q, cache=cache, layout=layout, block_table=block_table, heads_q=self.num_heads,
                                      max_seq_len=max_seq_len, num_splits=0, qpoint_dtype=rk.dtype,
                                      wait_for_pdl_writer=writer_pdl)
@@ -280,25 +297,82 @@ class BeyondPackedImpl:
         if ws is None:
             ws = _rt.allocate_runtime_workspace(spec, device=q.device)
             self._workspaces[spec] = ws
-        if seq_lens.dtype != torch.int32 or not seq_lens.is_contiguous():
-            seq_lens = seq_lens.to(torch.int32).contiguous()
+        # the current token is written first and then attended like any other (:2953-2969)
+        write_tokens_to_paged_cache(cache, layout, block_table, slots[:batch], k[:batch], v[:batch], q_points_k=qk,
+                                    q_points_v=qv, thresholds_k=tk, thresholds_v=tv, signal_pdl_dependents=writer_pdl,
+                                    require_fast=True)
         _rt.run_nonuniform_decode(spec=spec, q=q, cache=cache, layout=layout, block_table=block_table, seq_lens=seq_lens,
                                   k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=output[:batch], workspace=ws,
                                   softmax_scale=self.scale)
         return output
 
-    def _prefill(self, q, k, v, output, cache, layout, block_table, slots, q_starts, qk, tk, qv, tv):
-        # K/V are reconstructed in place so that attention sees exactly what the cache holds (:2481-2498)
-        write_tokens_to_paged_cache(cache, layout, block_table, slots, k, v, q_points_k=qk, q_points_v=qv,
-                                    thresholds_k=tk, thresholds_v=tv, k_dq_out=k, v_dq_out=v, require_fast=True)
+    def _dense_attention(self, q, k, v, output, q_starts, k_starts):
+        """Causal attention of every request's queries over its dense keys, the last query row
+        aligned with the last key (what the reference hands to FlashAttention's varlen call, a
+        library outside this path; here one scaled_dot_product_attention per request)."""
         rep = self.num_heads // self.num_kv_heads
         for i in range(len(q_starts) - 1):
             s, e = int(q_starts[i]), int(q_starts[i + 1])
+            ks, ke = int(k_starts[i]), int(k_starts[i + 1])
             if e <= s:
                 continue
             qi = q[s:e].transpose(0, 1).unsqueeze(0)
-            ki = k[s:e].repeat_interleave(rep, dim=1).transpose(0, 1).unsqueeze(0)
-            vi = v[s:e].repeat_interleave(rep, dim=1).transpose(0, 1).unsqueeze(0)
-            o = torch.nn.functional.scaled_dot_product_attention(qi, ki, vi, is_causal=True, scale=self.scale)
+            ki = k[ks:ke].repeat_interleave(rep, dim=1).transpose(0, 1).unsqueeze(0)
+            vi = v[ks:ke].repeat_interleave(rep, dim=1).transpose(0, 1).unsqueeze(0)
+            nq, nk = e - s, ke - ks
+            if nq == nk:
+                o = torch.nn.functional.scaled_dot_product_attention(qi, ki, vi, is_causal=True, scale=self.scale)
+            else:  # query row r sees keys 0 .. nk - nq + r
+                mask = torch.ones((nq, nk), dtype=torch.bool, device=q.device).tril(diagonal=nk - nq)
+                o = torch.nn.functional.scaled_dot_product_attention(qi, ki, vi, attn_mask=mask, scale=self.scale)
             output[s:e].copy_(o.squeeze(0).transpose(0, 1))
+
+    def _prefill(self, q, k, v, output, cache, layout, block_table, slots, q_starts, tables):
+        qk, tk, qv, tv = tables[:4]
+        # K/V are reconstructed in place so that attention sees exactly what the cache holds (:2481-2498)
+        write_tokens_to_paged_cache(cache, layout, block_table, slots, k, v, q_points_k=qk, q_points_v=qv,
+                                    thresholds_k=tk, thresholds_v=tv, k_dq_out=k, v_dq_out=v, require_fast=True)
+        self._dense_attention(q, k, v, output, q_starts, q_starts)
+        return output
+
+    def _chunked_prefill(self, q, k, v, output, cache, layout, block_table, seq_lens, slots, q_starts, seq_lens_cpu, tables):
+        """A chunk of every request's prompt behind context that is already cached (reference
+        ``_run_production_chunked_prefill_forward``, :2523-2625): the chunk is committed to the
+        packed cache, the whole context of every request is read back into one bounded dense
+        view, and the chunk's queries attend that view causally."""
+        qk, tk, qv, tv = tables[:4]
+        num_reqs = len(q_starts) - 1
+        total_k = sum(int(n) for n in seq_lens_cpu[:num_reqs])
+        itemsize = torch.empty((), dtype=q.dtype).element_size()
+        if 2 * total_k * self.num_kv_heads * self.head_size * itemsize > _CHUNKED_PREFILL_WORKSPACE_MB << 20:
+            raise NotImplementedError(
+                "Beyond production attention could not represent this mixed or chunked-prefill scheduler plan "
+                f"(its dense read-back view would exceed {_CHUNKED_PREFILL_WORKSPACE_MB} MB)."
+            )
+        held = self._dense_workspace
+        if held is None or held[0].shape[0] < total_k or held[0].dtype != q.dtype or held[0].device != q.device:
+            shape = (total_k, self.num_kv_heads, self.head_size)
+            held = self._dense_workspace = (torch.empty(shape, dtype=q.dtype, device=q.device),
+                                            torch.empty(shape, dtype=q.dtype, device=q.device))
+        dense_k, dense_v = held[0][:total_k], held[1][:total_k]
+        k_starts = [0]
+        for n in seq_lens_cpu[:num_reqs]:
+            k_starts.append(k_starts[-1] + int(n))
+        lens_gpu = seq_lens[:num_reqs]
+        if lens_gpu.dtype != torch.int32 or not lens_gpu.is_contiguous():
+            lens_gpu = lens_gpu.to(torch.int32).contiguous()
+        starts_gpu = torch.tensor(k_starts, dtype=torch.int32, device=q.device)
+        if slots.dtype != torch.int32 or not slots.is_contiguous():
+            slots = slots.to(torch.int32).contiguous()
+        if int(slots.numel()) != int(k.shape[0]):
+            raise ValueError("slot_mapping must contain one entry per chunked-prefill K/V token")
+        write_tokens_to_paged_cache(cache, layout, block_table, slots, k, v, q_points_k=qk, q_points_v=qv,
+                                    thresholds_k=tk, thresholds_v=tv, require_fast=True)
+        table = block_table[:num_reqs]
+        if table.dtype != torch.int32 or table.stride(-1) != 1:
+            table = table.to(torch.int32).contiguous()
+        dequantize_paged_kv_to_dense(cache, layout, table, lens_gpu, starts_gpu, dense_k, dense_v,
+                                     max_seq_len=max(int(n) for n in seq_lens_cpu[:num_reqs]),
+                                     q_points_k=qk, q_points_v=qv, stat_dtype=q.dtype)
+        self._dense_attention(q, dense_k, dense_v, output, q_starts, k_starts)
         return output

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define BKV_ABI_VERSION 1
+#define BKV_ABI_VERSION 2
 
 /* status codes */
 #define BKV_OK 0
@@ -48,7 +48,10 @@ extern "C" {
 
 /* flags */
 #define BKV_FLAG_PDL_TRIGGER 0x1   /* encode: signal dependent launch early          */
-#define BKV_FLAG_PDL_WAIT 0x2      /* decode: wait for the preceding kernel (PDL)    */
+#define BKV_FLAG_PDL_WAIT 0x2      /* decode: launched as a programmatic dependent of the
+                                      immediately preceding kernel, which must be the cache
+                                      writer: sequence lengths, block table and queries are
+                                      read before the wait and must come from older launches */
 #define BKV_FLAG_LINEAR_SEARCH 0x4 /* encode: count thresholds linearly (unsorted tables) */
 #define BKV_FLAG_KLEVELS_LANE_MAJOR 0x8 /* decode: K levels given as (Hkv,16,4)      */
 
@@ -85,10 +88,12 @@ int bkv_encode_sm100(const void* k, const void* v, int64_t k_stride_t, int64_t k
                      bkv_stream_t stream);
 
 /*
- * Fused paged split-KV decode attention over the packed cache.  Replaces
- * run_nonuniform_decode -> MixedInputFusedMultiHeadAttentionDecode (+ reducer)
- * (quant/fa4_cute/beyond_mixed_decode_runtime.py:520-612,
- *  quant/fa4_cute/beyond_mixed_decode_sm100.py:930-3214).
+ * Fused paged split-KV decode attention over the packed cache, general form: a
+ * (split, kv head, request) grid on CUDA cores that takes any page size and any supported
+ * head ratio.  Replaces run_nonuniform_decode -> MixedInputFusedMultiHeadAttentionDecode
+ * (+ reducer) (quant/fa4_cute/beyond_mixed_decode_runtime.py:520-612,
+ *  quant/fa4_cute/beyond_mixed_decode_sm100.py:930-3214) for an explicit split count.
+ * The production path is bkv_decode_stream_sm100 below (tensor cores, no split count).
  *
  * q ............. [batch][heads_q][128] q_dtype, head stride 128, batch stride given.
  * block_table ... int32 [batch][>= ceil(max seq_len / block_size)], row stride given.
@@ -99,6 +104,7 @@ int bkv_encode_sm100(const void* k, const void* v, int64_t k_stride_t, int64_t k
  * out_f32 ....... optional float32 copy of the un-rounded result (may be NULL).
  * o/m/l_partial . float32 workspaces [num_splits][batch][heads_q]([128]); only read
  *                 and written when num_splits > 1.
+ * softmax_scale . must be positive.
  * Split s of a request covers pages s, s+num_splits, ... of its block table row.
  */
 int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const void* cache,
@@ -107,8 +113,7 @@ int bkv_decode_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const v
                      const int32_t* seq_lens, const void* lvl_k, const void* lvl_v,
                      int table_dtype, void* out, int out_dtype, float* out_f32, float* o_partial,
                      float* m_partial, float* l_partial, int num_splits, int batch, int heads_q,
-                     int max_seq_len, float softmax_scale, int flags, int variant,
-                     bkv_stream_t stream);
+                     int max_seq_len, float softmax_scale, int flags, bkv_stream_t stream);
 
 /*
  * Test hook (no counterpart in the reference): the encoder divides by the group scale with
@@ -123,33 +128,66 @@ int bkv_selftest_division_sm100(uint64_t seed, int64_t count, int mode, unsigned
                                 bkv_stream_t stream);
 
 /*
- * Persistent form of bkv_decode_sm100: same inputs and results, different schedule.
+ * The production decode kernel: tensor cores, one persistent CTA per SM.
  *
  * Replaces the same reference launcher as bkv_decode_sm100
- * (quant/fa4_cute/beyond_mixed_decode_runtime.py:255-330 run_nonuniform_decode ->
- * compiled split kernel + combine).  Instead of a (split, head, request) grid whose split
- * count comes from the launch policy, one CTA per SM takes an equal share of all
- * (head, request, tile) work, so requests of any length mix keep every SM busy and the
- * decode tables are built once per CTA.  Requests that end up cut between workers leave
- * partials in `workspace`; a second kernel merges them.  num_splits does not exist here.
+ * (quant/fa4_cute/beyond_mixed_decode_runtime.py:520-612 run_nonuniform_decode ->
+ * compiled split kernel + reducer, quant/fa4_cute/beyond_mixed_decode_sm100.py:930-3214).
+ * Instead of a (split, head, request) grid whose split count comes from a launch policy,
+ * one CTA per SM takes an equal share of all (head, request, 16-token tile) work, so
+ * requests of any length mix keep every SM busy.  A request that ends up cut between workers
+ * leaves partials in `workspace`; the worker that finishes last merges them inside the same
+ * kernel.  There is no split count and no second launch.
  *
  * workspace / workspace_bytes: device scratch of at least
- * bkv_decode_stream_workspace_bytes() bytes (the bound depends on the current device
- * only, not on the shapes); contents need not be initialised and are overwritten.
- * Two calls that may overlap on the GPU need separate workspaces.
- * Returns BKV_ERR_UNSUPPORTED (launch nothing) for batch > 16384, more than 2^26 pages or
- * a page size the tensor-core kernel does not handle; use bkv_decode_sm100 then.
- * variant: 0 default configuration; 41 / 43 select 8 / 16 warps per CTA.
+ * bkv_decode_stream_workspace_bytes() bytes (the bound depends on the current device only).
+ * Before its FIRST use it must be prepared with bkv_decode_stream_workspace_init (or be
+ * zero-filled); the kernels leave it prepared, so one call per allocation is enough.  Two
+ * calls that may overlap on the GPU need separate workspaces.  If
+ * bkv_decode_device_status ever reports a non-zero status, prepare the workspace again.
+ * byte_tables: NULL, or the buffer filled by bkv_decode_tables_sm100 for these lvl_k /
+ * lvl_v (once per layer): the kernel then copies its look-up tables instead of building them.
+ * lvl_k / lvl_v must be 16-bit tables here (BKV_F16 or BKV_BF16; bf16 levels of magnitude
+ * 2^-14 .. 1 are exact in the kernel's fp16 tables); float32 tables return
+ * BKV_ERR_UNSUPPORTED.
+ * Returns BKV_ERR_UNSUPPORTED (launches nothing) for batch > 16384, more than 2^26 pages,
+ * more than 2^20 (kv head, request) pairs or a page size that is not 16 * 2^k; use
+ * bkv_decode_sm100 then.
+ * loader: 0 = 16-byte asynchronous copies (default), 1 = tensor copies of whole tile parts.
  */
 int64_t bkv_decode_stream_workspace_bytes(void);
+int bkv_decode_stream_workspace_init(void* workspace, int64_t workspace_bytes, bkv_stream_t stream);
 int bkv_decode_stream_sm100(const void* q, int64_t q_batch_stride, int q_dtype, const void* cache,
                             int64_t num_pages, int64_t page_stride_i32, int block_size,
                             int heads_kv, int stat_dtype, const int32_t* block_table,
                             int64_t block_table_stride, const int32_t* seq_lens,
                             const void* lvl_k, const void* lvl_v, int table_dtype, void* out,
                             int out_dtype, float* out_f32, void* workspace,
-                            int64_t workspace_bytes, int batch, int heads_q, int max_seq_len,
-                            float softmax_scale, int flags, int variant, bkv_stream_t stream);
+                            int64_t workspace_bytes, const void* byte_tables, int batch,
+                            int heads_q, int max_seq_len, float softmax_scale, int flags,
+                            int loader, bkv_stream_t stream);
+
+/*
+ * Decode-side table preparation, once per layer: expands the 16-level tables of every kv
+ * head into the byte-indexed look-up tables of bkv_decode_stream_sm100 (128 KiB per kv head,
+ * bkv_decode_tables_bytes(heads_kv) in all).  Takes the place of the per-launch table
+ * staging of the reference kernel (prepare_runtime_qpoints,
+ * quant/fa4_cute/beyond_mixed_decode_runtime.py:92-134, is likewise "once per layer").
+ * lvl_k / lvl_v / table_dtype / flags as for the decode call.
+ */
+int64_t bkv_decode_tables_bytes(int heads_kv);
+int bkv_decode_tables_sm100(const void* lvl_k, const void* lvl_v, int table_dtype, int heads_kv,
+                            int flags, void* tables, int64_t tables_bytes, bkv_stream_t stream);
+
+/*
+ * Host-only check of the persistent kernel's work partition (no device access; no counterpart
+ * in the reference): for `batch` requests of `tiles[b]` 16-token tiles each and
+ * `virtual_heads` heads on `sm_count` SMs it walks every worker's run the way the kernel does
+ * and compares where the parts of every cut request go with the list the merging worker
+ * derives.  Returns the number of requests that disagree (expected 0), -1 for bad arguments.
+ */
+int bkv_selftest_partition(const int32_t* tiles, int batch, int virtual_heads, int sm_count,
+                           int max_tiles_per_request);
 
 /*
  * bkv_combine_sm100 over packed records: split s is the block of rows*130 floats at
@@ -164,8 +202,8 @@ int bkv_combine_packed_sm100(const float* records, int num_splits, int64_t rows,
  * un-normalised partials (o, m natural-log, l) of every (request, query head) over the
  * positions [token_lo, min(token_hi, seq_len)), with all SMs busy even for one request
  * (the range call above runs one CTA per request and head).  No counterpart in the
- * reference, which has no KV-range sharding.  workspace as for bkv_decode_stream_sm100;
- * token_lo must be a multiple of block_size.
+ * reference, which has no KV-range sharding.  workspace, byte_tables and loader as for
+ * bkv_decode_stream_sm100; token_lo must be a multiple of block_size.
  */
 int bkv_decode_range_stream_sm100(const void* q, int64_t q_batch_stride, int q_dtype,
                                   const void* cache, int64_t num_pages, int64_t page_stride_i32,
@@ -174,8 +212,9 @@ int bkv_decode_range_stream_sm100(const void* q, int64_t q_batch_stride, int q_d
                                   const int32_t* seq_lens, const void* lvl_k, const void* lvl_v,
                                   int table_dtype, float* o_partial, float* m_partial,
                                   float* l_partial, void* workspace, int64_t workspace_bytes,
-                                  int batch, int heads_q, int token_lo, int token_hi,
-                                  float softmax_scale, int flags, int variant, bkv_stream_t stream);
+                                  const void* byte_tables, int batch, int heads_q, int token_lo,
+                                  int token_hi, float softmax_scale, int flags, int loader,
+                                  bkv_stream_t stream);
 
 /*
  * bkv_decode_sm100 for callers that cannot allocate device memory (no counterpart in
@@ -209,8 +248,8 @@ int bkv_decode_noalloc_sm100(const void* q, int64_t q_batch_stride, int q_dtype,
 
 /*
  * Diagnostic: reads and clears the device-side status word of the decode kernels
- * (0 = fine; 1 / 2 = a bounded wait inside the tensor-core kernel gave up after 2 s
- * instead of spinning forever).  Synchronises the device.  No counterpart in the
+ * (0 = fine; 2 = a bounded wait inside the tensor-core kernel gave up after 2 s instead of
+ * spinning forever; 3 = the kernel found an unexpected shared-memory layout and did nothing).  Synchronises the device.  No counterpart in the
  * reference.
  */
 int bkv_decode_device_status(int* status_out);

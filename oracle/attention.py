@@ -22,14 +22,19 @@ from .paged import PageGeometry, read_request
 
 def _attend(q: np.ndarray, k_hat: np.ndarray, v_hat: np.ndarray, scale: float, group: int):
     """q (Hq, D); k_hat/v_hat (S, Hkv, D) -> unnormalised o (Hq, D), m (Hq,), l (Hq,)."""
-    q64 = q.astype(np.float64)
-    k64 = np.repeat(k_hat.astype(np.float64), group, axis=1)  # (S, Hq, D)
-    v64 = np.repeat(v_hat.astype(np.float64), group, axis=1)
-    s = np.einsum("hd,shd->hs", q64, k64) * float(scale)
-    m = s.max(axis=1)
-    p = np.exp(s - m[:, None])
-    l = p.sum(axis=1)
-    o = np.einsum("hs,shd->hd", p, v64)
+    heads_q, dim = q.shape
+    o = np.zeros((heads_q, dim), dtype=np.float64)
+    m = np.zeros((heads_q,), dtype=np.float64)
+    l = np.zeros((heads_q,), dtype=np.float64)
+    for h in range(k_hat.shape[1]):  # the query heads of one group share their KV head
+        rows = slice(h * group, (h + 1) * group)
+        k64 = k_hat[:, h].astype(np.float64)
+        v64 = v_hat[:, h].astype(np.float64)
+        s = (q[rows].astype(np.float64) @ k64.T) * float(scale)
+        m[rows] = s.max(axis=1)
+        p = np.exp(s - m[rows, None])
+        l[rows] = p.sum(axis=1)
+        o[rows] = p @ v64
     return o, m, l
 
 

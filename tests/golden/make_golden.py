@@ -4,7 +4,9 @@ Python code (``quant/beyond_cute.py`` of wsxhjnb1/Beyond-KV-Cache) on CPU.
 Usage (needs the reference checkout; the fixtures themselves are committed, so the
 tests never need it):
 
-    BEYOND_REFERENCE=/path/to/Beyond-KV-Cache python tests/golden/make_golden.py
+    BEYOND_REFERENCE=/path/to/Beyond-KV-Cache python tests/golden/make_golden.py [kat writer config0 fakeqdq]
+
+(no names: all four files).
 
 Inputs come from ``numpy.random.default_rng`` (bit-stable across platforms) and are
 stored or check-summed next to the reference outputs.  Nothing here imports the
@@ -26,6 +28,7 @@ REPO = os.path.dirname(os.path.dirname(HERE))
 REF = os.environ.get("BEYOND_REFERENCE", os.path.join(os.path.dirname(REPO), "reference"))
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
+sys.path.insert(0, os.path.join(REF, "src"))
 sys.path.insert(0, REPO)
 
 import quant.beyond_cute as ref  # noqa: E402  (the reference module)
@@ -182,13 +185,43 @@ def config0_case() -> dict:
     return out
 
 
+def fakeqdq_case() -> dict:
+    """The training-equivalent fake quantise/dequantise path (float statistics, never rounded to
+    16 bits) as the reference's own layer evaluates it: ``UnifiedQuantLayer`` with per-group tables
+    (``src/beyond/quantization/layers.py:1398-1475``), the layer that ``_fake_quant_token_4d``
+    (``src/beyond/runtime/vllm/packed_backend.py:1081-1154``) is defined to agree with and that
+    ``quant/tests/test_pack_roundtrip.py:56-103`` compares the packed path against."""
+    from beyond.quantization.layers import UnifiedQuantLayer
+
+    out = {}
+    B, S, H, D = 2, 13, 2, 128
+    rng = np.random.default_rng(505)
+    x32 = rng.standard_normal((B, S, H, D)).astype(np.float32)
+    x32[..., 7] *= 8.0
+    layer = UnifiedQuantLayer(num_bits=4, group_size=32, grouping_dim="token", quant_width=H * D)
+    levels, thresholds = layer.materialize_quant_tables()
+    out["fq_x32"] = x32
+    out["fq_levels"] = levels.detach().float().numpy()
+    out["fq_thresholds"] = thresholds.detach().float().numpy()
+    with torch.no_grad():
+        out["fq_y32"] = layer(torch.from_numpy(x32).reshape(B, S, H * D)).reshape(B, S, H, D).numpy()
+        for name, dt in (("f16", torch.float16), ("bf16", torch.bfloat16)):
+            y = layer(torch.from_numpy(x32).to(dt).reshape(B, S, H * D)).reshape(B, S, H, D)
+            out[f"fq_y_bits_{name}"] = bits16(y)
+    return out
+
+
 def main() -> None:
     torch.manual_seed(0)
-    np.savez_compressed(os.path.join(HERE, "kat.npz"), **kat_cases(), **layout_cases())
-    np.savez_compressed(os.path.join(HERE, "writer.npz"), **writer_cases())
-    np.savez_compressed(os.path.join(HERE, "config0.npz"), **config0_case())
-    for f in ("kat.npz", "writer.npz", "config0.npz"):
-        print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
+    makers = {
+        "kat": lambda: {**kat_cases(), **layout_cases()},
+        "writer": writer_cases,
+        "config0": config0_case,
+        "fakeqdq": fakeqdq_case,
+    }
+    for name in sys.argv[1:] or list(makers):
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **makers[name]())
+        print(f"{name}.npz", os.path.getsize(os.path.join(HERE, f"{name}.npz")), "bytes")
 
 
 if __name__ == "__main__":

@@ -32,9 +32,10 @@ def oracle_cache(seq_lens, heads, block_size, kind, seed, thr_k, thr_v, spare=3)
     perm = rng.permutation(total)
     bt = np.full((len(seq_lens), width), -1, dtype=np.int32)
     geo = oracle.PageGeometry(block_size, heads, 128)
+    # pages start out as random words, as in the reference's own tests (quant/tests/test_paged.py:528-536):
+    # whatever a page holds beyond the positions written below - NaN and infinite statistics included -
+    # must not reach the attention output
     cache = rng.integers(-(2**31), 2**31, (total, geo.block_i32)).astype(np.int32)
-    # unwritten slots must still hold finite statistics for the masked tail of a page
-    cache[:] = 0
     cursor = 0
     for b, n in enumerate(seq_lens):
         bt[b, : pages[b]] = perm[cursor : cursor + pages[b]]
@@ -48,12 +49,15 @@ def oracle_cache(seq_lens, heads, block_size, kind, seed, thr_k, thr_v, spare=3)
         v = oracle.stat_to_f32(oracle.round_to_stat(v, kind), kind)
         pos = np.arange(n)
         slots = bt[b].astype(np.int64)[pos // block_size] * block_size + pos % block_size
-        oracle.write_pages(cache, geo, slots, k, v, thresholds_k=thr_k, thresholds_v=thr_v, stat=kind)
+        for c0 in range(0, n, 8192):  # the oracle's temporaries grow with the rows of a call
+            c1 = min(n, c0 + 8192)
+            oracle.write_pages(cache, geo, slots[c0:c1], k[c0:c1], v[c0:c1], thresholds_k=thr_k, thresholds_v=thr_v, stat=kind)
     return cache, bt
 
 
-def gpu_decode(q, cache, bt, seq_lens, heads_kv, block_size, lk, lv, *, kind, splits=0, variant=0, max_seq_len=None, scale=None):
-    """Run the product launcher; returns (out in q.dtype, out_f32) as CPU tensors."""
+def gpu_decode(q, cache, bt, seq_lens, heads_kv, block_size, lk, lv, *, kind, splits=0, loader=0, max_seq_len=None, scale=None):
+    """Run the product launcher (``splits=0``: persistent schedule, else the split grid with
+    that count); returns (out in q.dtype, out_f32, spec), the tensors on the CPU."""
     dev = torch.device("cuda")
     layout = PagedLayout.build_hnd(block_size, heads_kv, 128, 4, 32, 32)
     qd = q.to(dev)
@@ -71,6 +75,6 @@ def gpu_decode(q, cache, bt, seq_lens, heads_kv, block_size, lk, lv, *, kind, sp
     rt.run_nonuniform_decode(spec=spec, q=qd, cache=cache_d, layout=layout, block_table=bt_d, seq_lens=lens_d,
                              k_qpoints_lane_major=rk, v_qpoints_code_major=rv, out=out, workspace=ws,
                              softmax_scale=scale if scale is not None else synth.softmax_scale(),
-                             stat_dtype=KIND_TO_DTYPE[kind], out_f32=out32, variant=variant)
+                             stat_dtype=KIND_TO_DTYPE[kind], out_f32=out32, loader=loader)
     torch.cuda.synchronize()
     return out.cpu(), out32.cpu(), spec

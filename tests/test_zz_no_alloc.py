@@ -5,13 +5,15 @@ inside somebody else's capture region, or an embedder with a fixed memory arena 
 `bkv_decode_noalloc_sm100` keeps its split workspace in a fixed array inside the library.
 This test drives it through the C ABI twice in a row (the array is shared and keeps the
 previous call's contents) and requires the same output as the regular entry point, which
-gets a caller-allocated workspace.  The result must not depend on whether other tests ran
-before it in the same process."""
+gets a caller-allocated workspace, and - so that the test stands on its own - the CPU oracle
+within the decode tolerance.  The result must not depend on whether other tests ran before it
+in the same process."""
 
 import numpy as np
 import pytest
 import torch
 
+import oracle
 from beyond_kv_cache_b200 import _lib, synth
 from tests.helpers import oracle_cache, tables
 
@@ -25,8 +27,6 @@ def _call(fn, extra_ws, q, cache, bt, lens, lk, lv, out, out32, splits, max_seq_
             out.data_ptr(), _lib.BKV_BF16, out32.data_ptr()]
     args += extra_ws
     args += [splits, q.shape[0], q.shape[1], max_seq_len, synth.softmax_scale(), 0]
-    if fn == "bkv_decode_sm100":
-        args.append(0)  # variant
     args.append(_lib.current_stream(q.device))
     _lib.call(fn, *args)
 
@@ -54,6 +54,10 @@ def test_noalloc_entry_matches_workspace_entry_twice():
             assert torch.equal(got32, want32)
             assert torch.equal(got, want)
             assert float(want32.abs().max()) > 0
+            truth = oracle.decode_attention(q.float().cpu().numpy(), cache_np, oracle.PageGeometry(16, 2), bt_np, lens,
+                                            levels_k=lk.float().numpy(), levels_v=lv.float().numpy(),
+                                            softmax_scale=synth.softmax_scale(), stat="bf16")
+            assert float(np.abs(got32.cpu().numpy() - truth).max()) <= 2e-3
 
 
 def test_noalloc_entry_rejects_oversized_launch():
