@@ -50,6 +50,12 @@ SIGNATURES = {
     "bkv_combine_packed_sm100": [_P, _I, _L, _P, _I, _P, _P],
     "bkv_decode_range_stream_sm100": [_P, _L, _I, _P, _L, _L, _I, _I, _I, _P, _L, _P, _P, _P, _I, _P, _P,
                                       _P, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+    "bkv_kv_exchange_bytes": [_I, _L],
+    "bkv_kv_exchange_alloc": [_L, _P, _P],
+    "bkv_kv_exchange_open": [_P, _P],
+    "bkv_kv_exchange_close": [_P],
+    "bkv_kv_exchange_free": [_P],
+    "bkv_kv_exchange_merge_sm100": [_P, _L, _P, _I, _I, _I, _L, _P, _I, _P, _P, _P],
     "bkv_readback_sm100": [_P, _L, _L, _I, _I, _I, _P, _L, _L, _P, _P, _I, _I, _P, _P, _I, _I, _I,
                            _P, _P, _I, _P],
     "bkv_decode_dense_sm100": [_P, _L, _I, _P, _P, _I, _L, _I, _I, _P, _L, _P, _P, _I, _P, _P, _P,
@@ -88,7 +94,7 @@ def load() -> ctypes.CDLL:
             fn.argtypes = argtypes
             if name in ("bkv_status_string", "bkv_last_cuda_error"):
                 fn.restype = _c.c_char_p
-            elif name in ("bkv_decode_stream_workspace_bytes", "bkv_decode_tables_bytes"):
+            elif name in ("bkv_decode_stream_workspace_bytes", "bkv_decode_tables_bytes", "bkv_kv_exchange_bytes"):
                 fn.restype = _L
             else:
                 fn.restype = _I

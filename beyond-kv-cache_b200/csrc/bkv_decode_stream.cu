@@ -85,8 +85,8 @@ constexpr int kMaxCtas = (kPrefixAddr - kBoundAddr) / 8 - 1;
 static_assert(kMaxCtas >= 148, "the share boundaries of a full B200 grid fit behind the ring");
 constexpr uint32_t kFullBar = kSmemBase;          // 8 B each
 constexpr uint32_t kChunkTot = kSmemBase + 512;   // int[32] scan scratch
-constexpr uint32_t kPendList = kSmemBase + 640;   // int[16 warps][4]: cut requests this warp has to merge at the end
-constexpr uint32_t kPendCount = kSmemBase + 896;  // int[16 warps]
+constexpr uint32_t kPendList = kSmemBase + 640;   // int[64]: cut requests whose last part a warp of this CTA wrote
+constexpr uint32_t kPendCount = kSmemBase + 896;  // int: entries of the list
 constexpr uint32_t kPendCta = kSmemBase + 960;    // int[2]: the same for the CTA as a whole, one per phase (-1: none)
 constexpr uint32_t kLevels = kSmemBase + 1280;    // fp16 [K|V][4][16]
 constexpr int kTableBarIndex = 63;               // the last of the 64 barrier words: byte tables landed
@@ -178,6 +178,7 @@ struct MergeIo {
 // six at a time.  The calling warp takes the batches begin, begin+step, ...; lane l accumulates
 // query head l>>3 of the quad, dimensions 16*(l&7) .. +15.  The partials were written by other
 // SMs, so they are read from L2.
+template <int NW>
 __device__ __noinline__ void merge_parts(const MergeIo io, const part::Plan pl, const int vh, const int pb, const int pe,
                                          const int begin, const int step) {
   constexpr uint32_t kAll = 0xffffffffu;
@@ -189,17 +190,19 @@ __device__ __noinline__ void merge_parts(const MergeIo io, const part::Plan pl, 
   constexpr int kBatch = 6;  // parts loaded at once (one L2 round trip)
   int batch = 0;
   const int64_t g0 = static_cast<int64_t>(vh) * pl.Tb + pb, g1 = static_cast<int64_t>(vh) * pl.Tb + pe;
-  for (int c0 = 0; c0 < pl.C; c0 += 32) {
+  int c_lo, c_hi;
+  part::ctas_near_head(pl, vh, &c_lo, &c_hi);  // the CTAs that can hold tiles of this head: usually one round of 32
+  for (int c0 = c_lo; c0 <= c_hi; c0 += 32) {
     // which of these 32 CTAs hold tiles of the request at all: two loads and two compares per lane
     int64_t ga = 0, gb = 0;
-    if (c0 + lane < pl.C) {
+    if (c0 + lane <= c_hi) {
       ga = io.bounds[c0 + lane];
       gb = io.bounds[c0 + lane + 1];
     }
     const bool meets = ga < g1 && gb > g0;
     if (!__any_sync(kAll, meets)) continue;
     part::CtaParts cp = {0u, 0, 0, 0};
-    if (meets) cp = part::cta_parts(pl, ga, gb, vh, pb, pe);
+    if (meets) cp = part::cta_parts<NW>(pl, ga, gb, vh, pb, pe);
     const int cnt = __popc(cp.mask);
     int incl = cnt;
 #pragma unroll
@@ -248,8 +251,7 @@ __device__ __noinline__ void merge_parts(const MergeIo io, const part::Plan pl, 
       for (int u = 0; u < kBatch; ++u) {
         if (!(l2[u] > 0.f)) continue;
         const float Mn = fmaxf(M, m2[u]);
-        const float a = (M == -CUDART_INF_F) ? 0.f : exp2f(M - Mn);
-        const float wgt = exp2f(m2[u] - Mn);
+        const float a = fast_exp2(M - Mn), wgt = fast_exp2(m2[u] - Mn);  // exp2(-inf) = 0: the first part
         den = den * a + l2[u] * wgt;
 #pragma unroll
         for (int i = 0; i < 16; ++i) num[i] = num[i] * a + o2[u][i] * wgt;
@@ -295,6 +297,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
                          const __grid_constant__ CUtensorMap map_stat, const __grid_constant__ CUtensorMap map_vstat) {
   static_assert(STAGES <= 4, "cp_async_wait_pending handles up to three groups in flight");
   static_assert(NW * STAGES < kTableBarIndex, "the last barrier word belongs to the byte tables");
+  static_assert(4 * NW <= 64, "every warp can be the last of two cut requests in each of the two phases");
   using R = Ring<NW, STAGES>;
   const DecodeParams& p = sp.d;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -319,6 +322,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
   const int lo = max(p.token_lo, 0);
   const int page_lo = lo / BS;
 
+  pdl_launch_dependents();  // a kernel launched as this grid's programmatic dependent may be set up now
   if (tid == 0) {
     for (int i = 0; i < NW * STAGES; ++i) mbar_init(kFullBar + 8 * i, 1);
     mbar_init(kFullBar + 8 * kTableBarIndex, 1);
@@ -326,7 +330,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
     reinterpret_cast<int*>(gptr(kPendCta))[0] = -1;
     reinterpret_cast<int*>(gptr(kPendCta))[1] = -1;
   }
-  if (tid < 16) reinterpret_cast<int*>(gptr(kPendCount))[tid] = 0;
+  if (tid == 0) reinterpret_cast<int*>(gptr(kPendCount))[0] = 0;
 
   // ---- tiles before every request (exclusive prefix sum over the batch) ------------------
   const bool planned = B > kMaxBatch;
@@ -545,6 +549,12 @@ __global__ void __maxnreg__(max_regs_for(NW))
       return phys | (static_cast<uint32_t>(k & (tiles_per_page - 1)) << kMaxPagesLog2);
     };
     uint32_t meta_cur = fetch_meta(0), meta_nxt = fetch_meta(32);
+    if (work) {  // the queries of the run's first request: under way while the tables are set up
+      const int esize = p.q_dtype == BKV_F32 ? 4 : 2;
+      const char* const fq = reinterpret_cast<const char*>(p.q) +
+                             (static_cast<int64_t>(request_of(wa)) * p.q_batch_stride + static_cast<int64_t>(hq0) * kHeadDim) * esize;
+      if (lane * 128 < nh * kHeadDim * esize) asm volatile("prefetch.global.L2 [%0];" ::"l"(fq + lane * 128));
+    }
     auto issue = [&](int j, int stage) {  // j-th tile of the run into ring stage `stage`
       if (j != 0 && (j & 31) == 0) {
         meta_cur = meta_nxt;
@@ -1012,11 +1022,11 @@ __global__ void __maxnreg__(max_regs_for(NW))
           int* const cnt_b = sp.ws_cnt + (static_cast<int64_t>(vh) * B + b);
           if (atomicAdd(cnt_b, kend - k0) + (kend - k0) == nb) {
             *cnt_b = 0;  // nobody else touches it any more: ready for the next launch
-            // the merge itself waits until this warp has streamed all its tiles (at most two cut
-            // requests per phase end up here): no call, and nothing it would clobber, in this loop
-            int* const n_pend = reinterpret_cast<int*>(gptr(kPendCount)) + warp;
-            reinterpret_cast<int*>(gptr(kPendList))[warp * 4 + *n_pend] = vh * B + b;
-            *n_pend += 1;
+            // the merge itself waits until the CTA has streamed all its tiles and is then dealt to
+            // whichever warp is next (at most two cut requests per warp and phase end up here): no
+            // call, and nothing a call would clobber, in this loop
+            const int at = atomicAdd(reinterpret_cast<int*>(gptr(kPendCount)), 1);
+            reinterpret_cast<int*>(gptr(kPendList))[at] = vh * B + b;
           }
         }
       }
@@ -1127,16 +1137,15 @@ __global__ void __maxnreg__(max_regs_for(NW))
   // over, so the call clobbers nothing that matters and the ring space is free.
   {
     const int hvq = quads;
-    __syncwarp();
-    const int n_pend = reinterpret_cast<const int*>(gptr(kPendCount))[warp];
-    for (int e = 0; e < n_pend; ++e) {
-      const int item = reinterpret_cast<const int*>(gptr(kPendList))[warp * 4 + e];
+    __syncthreads();  // every warp is through with its tiles: the list is complete, the ring space is free
+    const int n_pend = reinterpret_cast<const int*>(gptr(kPendCount))[0];
+    for (int e = warp; e < n_pend; e += NW) {
+      const int item = reinterpret_cast<const int*>(gptr(kPendList))[e];
       const int vh = item / B, b = item - vh * B;
       const int head = vh / hvq, quad = vh - head * hvq;
-      merge_parts(make_io(nullptr, static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4, min(4, gqa - quad * 4)),
-                  make_plan(), vh, prefix[b], prefix[b + 1], 0, 1);
+      merge_parts<NW>(make_io(nullptr, static_cast<int64_t>(b) * p.heads_q + head * gqa + quad * 4, min(4, gqa - quad * 4)),
+                      make_plan(), vh, prefix[b], prefix[b + 1], 0, 1);
     }
-    __syncthreads();  // every warp is through with its tiles: the ring space is free
     for (int ph = 0; ph < 2; ++ph) {
       const int item = reinterpret_cast<const int*>(gptr(kPendCta))[ph];
       if (item < 0) continue;  // uniform over the CTA
@@ -1147,7 +1156,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
       float* const rec = reinterpret_cast<float*>(gptr(kRingLoS));
       constexpr int kRec = 4 * kHeadDim + 8;
       __syncthreads();
-      merge_parts(make_io(rec + warp * kRec, 0, nh), make_plan(), vh, prefix[b], prefix[b + 1], warp, NW);
+      merge_parts<NW>(make_io(rec + warp * kRec, 0, nh), make_plan(), vh, prefix[b], prefix[b + 1], warp, NW);
       __syncthreads();
       // ... and the CTA folds the NW records
       for (int idx = tid; idx < 4 * kHeadDim; idx += NW * 32) {

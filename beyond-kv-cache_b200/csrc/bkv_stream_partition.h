@@ -128,8 +128,11 @@ struct CtaParts {
   int starts;     // 1: the lowest part of the mask begins the request (slot 1 instead of slot 0)
 };
 
-// (ga, gb: the share of the CTA, from share_of or from a table of the share boundaries)
+// (ga, gb: the share of the CTA, from share_of or from a table of the share boundaries; NWT: the
+// warps per CTA when known at compile time, which turns the divisions of the loop into multiplications)
+template <int NWT = 0>
 BKV_HD CtaParts cta_parts(const Plan& pl, int64_t ga, int64_t gb, int vh, int pb, int pe) {
+  const int NW = NWT > 0 ? NWT : pl.NW;
   CtaParts r = {0u, 0, 0, 0};
   // the span of this share inside head vh, and which of the share's (at most two) heads that is:
   // the first one unless the share begins before the head (no division needed for either)
@@ -151,8 +154,8 @@ BKV_HD CtaParts cta_parts(const Plan& pl, int64_t ga, int64_t gb, int vh, int pb
     return r;
   }
   int wa = s.first;
-  for (int w = 0; w < pl.NW; ++w) {
-    const int wb = run_begin(s, pl.NW, w + 1);
+  for (int w = 0; w < NW; ++w) {
+    const int wb = run_begin(s, NW, w + 1);
     const int i0 = wa > pb ? wa : pb, i1 = wb < pe ? wb : pe;
     if (i1 > i0) {
       if (r.mask == 0u) r.starts = i0 == pb;

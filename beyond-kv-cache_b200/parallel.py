@@ -8,13 +8,18 @@ parallelism is delegated to vLLM).  Two shardings are provided here:
   (:func:`shard_requests`).
 * **KV-range split of one long sequence** — rank ``r`` owns a contiguous, page-aligned
   range of positions, runs the decode kernel over it and produces an un-normalised
-  partial ``(o, m, l)`` per (request, query head); the partials (16.6 KB per rank for 32
-  heads) are all-gathered and merged with the log-sum-exp combine kernel, "splits =
-  world size" (:func:`decode_kv_range_split`).
+  partial ``(o, m, l)`` per (request, query head).  The partials (16.6 KB per rank for 32
+  heads) are exchanged and merged by log-sum-exp, "splits = world size"
+  (:func:`decode_kv_range_split`): with a :class:`KvRangeExchange` every rank stores its
+  record straight into the other ranks' receive buffers over NVLink and one kernel pushes,
+  waits (bounded) and merges; without one the records travel in one NCCL all-gather and the
+  combine kernel merges them.  ``torch.distributed`` is used for set-up and for that
+  all-gather only.
 """
 
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 import torch
@@ -126,6 +131,75 @@ def decode_range_partial(
     return o, m, l
 
 
+class KvRangeExchange:
+    """Receive buffers of the pushed KV-range exchange, one per rank, mapped into every other
+    rank of the node through CUDA IPC (``bkv_kv_exchange_*``).  Set-up is collective: every rank
+    of ``group`` constructs the object at the same point (the IPC handles travel through
+    ``all_gather_object``); after that a step needs no collective.  ``rows`` = batch x query
+    heads of the decode bucket.  ``close()`` is collective too."""
+
+    def __init__(self, rows: int, device: torch.device, group=None, timeout_s: float = 2.0):
+        lib = _lib.load()
+        self.group, self.rows, self.device = group, int(rows), torch.device(device)
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.step = 0
+        self._own = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            nbytes = int(lib.bkv_kv_exchange_bytes(self.world, self.rows))
+            _lib.call("bkv_kv_exchange_alloc", nbytes, ctypes.byref(self._own), handle)
+            handles = [bytes(handle)]
+            if self.world > 1:
+                handles = [None] * self.world
+                dist.all_gather_object(handles, bytes(handle), group=group)
+            self._peers = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self._peers.append(self._own.value)
+                    continue
+                peer = ctypes.c_void_p()
+                _lib.call("bkv_kv_exchange_open", (ctypes.c_ubyte * 64).from_buffer_copy(handles[r]), ctypes.byref(peer))
+                self._peers.append(peer.value)
+        self._peer_array = (ctypes.c_uint64 * self.world)(*self._peers)
+        self.status = torch.zeros((1,), dtype=torch.int32, device=self.device)
+        self.record = torch.empty((self.rows * 130,), dtype=torch.float32, device=self.device)
+        if self.world > 1:
+            dist.barrier(group=group)  # every buffer is mapped everywhere before the first push
+
+    def views(self):
+        """(o, m, l) views of the record the range decode writes."""
+        r = self.rows
+        return self.record[: r * 128].view(r, 128), self.record[r * 128 : r * 129], self.record[r * 129 :]
+
+    def merge(self, out: torch.Tensor, out_f32: Optional[torch.Tensor] = None) -> None:
+        """Push this rank's record, wait for the others' and merge into ``out`` (one kernel)."""
+        self.step += 1
+        _lib.call("bkv_kv_exchange_merge_sm100", self.record.data_ptr(), self.rows, self._peer_array, self.world, self.rank,
+                  self.step, self.timeout_ns, out.data_ptr(), _lib.dtype_code(out.dtype), _lib.ptr(out_f32),
+                  self.status.data_ptr(), _lib.current_stream(self.device))
+
+    def check(self) -> None:
+        """Host-side check (synchronises): raises when a wait of an earlier step ran out."""
+        if int(self.status.item()) != 0:
+            raise _lib.BkvError("bkv_kv_exchange_merge_sm100", 1, "a peer's record did not arrive within the time limit")
+
+    def close(self) -> None:
+        if self._own.value is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody pushes any more
+        for r, peer in enumerate(self._peers):
+            if r != self.rank:
+                _lib.call("bkv_kv_exchange_close", ctypes.c_void_p(peer))
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody maps this buffer any more
+        _lib.call("bkv_kv_exchange_free", self._own)
+        self._own = ctypes.c_void_p()
+
+
 def decode_kv_range_split(
     q: torch.Tensor,
     cache: torch.Tensor,
@@ -141,23 +215,31 @@ def decode_kv_range_split(
     softmax_scale: float,
     stat_dtype: Optional[torch.dtype] = None,
     group=None,
+    exchange: Optional[KvRangeExchange] = None,
+    out_f32: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Decode attention of a batch whose KV positions are split across the ranks of
     ``group``: this rank attends ``[token_lo, token_hi)`` from its own pages and leaves one
-    packed record ``o | m | l`` (rows x 130 float32); the records are all-gathered in ONE
-    collective (NCCL over NVLink) and merged on every rank into ``out``
+    packed record ``o | m | l`` (rows x 130 float32).  With ``exchange`` the records are pushed
+    into the peers' buffers and merged by one kernel; without it they are all-gathered in ONE
+    NCCL collective and merged by the combine kernel, on every rank, into ``out``
     ``(batch, heads_q, 128)``.  ``q`` must be identical on all ranks.  Buffers are kept per
     (device, rows, world), so steady-state calls allocate nothing."""
     batch, heads_q = int(q.shape[0]), int(q.shape[1])
     rows = batch * heads_q
     world = dist.get_world_size(group) if dist.is_initialized() else 1
-    key = (q.device.type, q.device.index, rows, world)
-    bufs = _RECORDS.get(key)
-    if bufs is None:
-        rec = torch.empty((rows * 130,), dtype=torch.float32, device=q.device)
-        every = torch.empty((world * rows * 130,), dtype=torch.float32, device=q.device) if world > 1 else rec
-        bufs = _RECORDS[key] = (rec, every)
-    rec, every = bufs
+    if exchange is not None:
+        if exchange.rows != rows or exchange.world != world:
+            raise ValueError("the exchange was set up for another bucket (rows) or group")
+        rec, every = exchange.record, None
+    else:
+        key = (q.device.type, q.device.index, rows, world)
+        bufs = _RECORDS.get(key)
+        if bufs is None:
+            rec = torch.empty((rows * 130,), dtype=torch.float32, device=q.device)
+            every = torch.empty((world * rows * 130,), dtype=torch.float32, device=q.device) if world > 1 else rec
+            bufs = _RECORDS[key] = (rec, every)
+        rec, every = bufs
     o, m, l = rec[: rows * 128].view(rows, 128), rec[rows * 128 : rows * 129], rec[rows * 129 :]
     if q_points_k.dtype != q_points_v.dtype:
         q_points_k, q_points_v = q_points_k.float(), q_points_v.float()
@@ -173,10 +255,13 @@ def decode_kv_range_split(
         o.data_ptr(), m.data_ptr(), l.data_ptr(), ws.data_ptr(), int(ws.numel()), None, batch, heads_q,
         int(token_lo), int(token_hi), float(softmax_scale), 0, 0, _lib.current_stream(q.device),
     )
+    if exchange is not None:
+        exchange.merge(out, out_f32)
+        return out
     if world > 1:
         dist.all_gather_into_tensor(every, rec, group=group)  # rank-major records
     _lib.call("bkv_combine_packed_sm100", every.data_ptr(), world, rows, out.data_ptr(), _lib.dtype_code(out.dtype),
-              None, _lib.current_stream(q.device))
+              _lib.ptr(out_f32), _lib.current_stream(q.device))
     return out
 
 

@@ -391,6 +391,8 @@ def run_nonuniform_decode(
             spec.batch_size, spec.heads_q, spec.max_seq_len,
             float(softmax_scale), flags, int(loader), _lib.current_stream(q.device),
         )
+        if os.environ.get("BEYOND_SM100_CHECK_STATUS") == "1" and not torch.cuda.is_current_stream_capturing():
+            check_device_status()
         return out
     if loader:
         raise ValueError("the tile loader is a choice of the persistent schedule; this bucket uses the split grid")
@@ -411,6 +413,29 @@ def run_nonuniform_decode(
         float(softmax_scale), flags, _lib.current_stream(q.device),
     )
     return out
+
+
+_STATUS_TEXT = {
+    2: "a bounded wait inside the decode kernel gave up (a copy into shared memory never completed); "
+       "the outputs of that launch are incomplete and its workspace must be prepared again",
+    3: "the decode kernel found its shared memory at an unexpected address and did nothing",
+}
+
+
+def check_device_status() -> None:
+    """Read (and clear) the device-side status word of the decode kernels and raise ``BkvError``
+    when a launch since the last check reported a failure.  The kernels never hang or trap: a wait
+    that cannot complete runs into its time limit, sets this word and lets the launch finish, so the
+    host has to look.  Synchronises the device - call it between steps, not inside a capture.
+    ``run_nonuniform_decode`` calls it after every launch when ``BEYOND_SM100_CHECK_STATUS=1``
+    (a debugging aid; it serialises host and device)."""
+    import ctypes
+
+    status = ctypes.c_int(0)
+    _lib.call("bkv_decode_device_status", ctypes.byref(status))
+    if status.value != 0:
+        raise _lib.BkvError("bkv_decode_device_status", status.value,
+                            _STATUS_TEXT.get(status.value, "unknown device status"))
 
 
 def clear_compiled_runtime_cache() -> None:

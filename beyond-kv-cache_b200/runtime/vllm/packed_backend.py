@@ -82,6 +82,31 @@ class BeyondPackedSpec:
         return self.real_page_size_bytes
 
 
+_VLLM_SPEC_CLASS = None
+
+
+def vllm_spec_class():
+    """``BeyondPackedSpec`` as a subclass of the installed vLLM's ``FullAttentionSpec`` (what the
+    reference declares, :473-486), so that vLLM's cache managers and allocator accept it; built on
+    first use because importing vLLM is slow and this module must work without it.  Raises
+    ImportError when vLLM (or that class) is not importable."""
+    global _VLLM_SPEC_CLASS
+    if _VLLM_SPEC_CLASS is None:
+        from vllm.v1.kv_cache_interface import FullAttentionSpec
+
+        @dataclass(frozen=True, kw_only=True)
+        class BeyondPackedVllmSpec(FullAttentionSpec):
+            """KV-cache spec of the packed layout: the cache is a flat ``(num_blocks, block_i32)`` int32
+            buffer, so a page is ``block_i32 * 4`` bytes whatever dtype and head size suggest."""
+
+            @property
+            def real_page_size_bytes(self) -> int:
+                return _paged_layout(self.block_size, self.num_kv_heads, self.head_size).block_i32 * 4
+
+        _VLLM_SPEC_CLASS = BeyondPackedVllmSpec
+    return _VLLM_SPEC_CLASS
+
+
 class BeyondPackedBackend:
     """Static description of the backend (reference :4836-4888)."""
 

@@ -1,9 +1,9 @@
 """Registers the packed backend with vLLM (reference ``src/beyond/runtime/vllm/registration.py``).
 
 Done here: the ``CUSTOM`` slot of vLLM's attention-backend registry points at
-``BeyondPackedBackend``; ``BeyondPackedSpec`` caches are managed by the stock full-attention
-manager; ``Attention.get_kv_cache_spec`` returns a ``BeyondPackedSpec`` for layers served by
-the backend.  Not done here: the reference's scheduler, static-buffer, replay-warm-up and
+``BeyondPackedBackend``; caches described by the packed spec (a subclass of vLLM's
+``FullAttentionSpec``, ``packed_backend.vllm_spec_class``) are managed by the stock full-attention
+manager; ``Attention.get_kv_cache_spec`` returns that spec for layers served by the backend.  Not done here: the reference's scheduler, static-buffer, replay-warm-up and
 graph-bucket patches of vLLM internals (reference `:23-25, :59`), which are serving glue
 outside the packed-KV path.
 """
@@ -30,7 +30,8 @@ def register_backend() -> bool:
     from vllm.v1.core.single_type_kv_cache_manager import FullAttentionManager, spec_manager_map
 
     # one full-attention cache per layer, whatever its byte layout
-    spec_manager_map.setdefault(backend.BeyondPackedSpec, FullAttentionManager)
+    spec_cls = backend.vllm_spec_class()
+    spec_manager_map.setdefault(spec_cls, FullAttentionManager)
 
     from vllm.model_executor.layers.attention.attention import Attention
     from vllm.v1.attention.backend import AttentionType
@@ -43,8 +44,8 @@ def register_backend() -> bool:
                 return stock(self, vllm_config)
             if self.attn_type != AttentionType.DECODER:
                 raise AssertionError("BeyondPacked only supports DECODER attention")
-            return backend.BeyondPackedSpec(block_size=vllm_config.cache_config.block_size, num_kv_heads=self.num_kv_heads,
-                                            head_size=self.head_size, dtype=torch.int32)
+            return spec_cls(block_size=vllm_config.cache_config.block_size, num_kv_heads=self.num_kv_heads,
+                            head_size=self.head_size, dtype=torch.int32)
 
         get_kv_cache_spec._beyond_patched = True
         Attention.get_kv_cache_spec = get_kv_cache_spec

@@ -3,8 +3,8 @@
  *
  * One shared library, libbkv_sm100.so, exports the entry points below.  They take
  * raw device pointers, sizes, element strides and a CUDA stream handle; they never
- * allocate, never synchronise and never throw: every call returns BKV_OK or a
- * negative status (see bkv_status_string).  Launch errors reported by the CUDA
+ * allocate (bkv_kv_exchange_alloc, a set-up call, is the one exception), never synchronise
+ * and never throw: every call returns BKV_OK or a negative status (see bkv_status_string).  Launch errors reported by the CUDA
  * runtime are returned as BKV_ERR_CUDA and the message is kept per thread
  * (bkv_last_cuda_error).
  *
@@ -215,6 +215,35 @@ int bkv_decode_range_stream_sm100(const void* q, int64_t q_batch_stride, int q_d
                                   const void* byte_tables, int batch, int heads_q, int token_lo,
                                   int token_hi, float softmax_scale, int flags, int loader,
                                   bkv_stream_t stream);
+
+/*
+ * Exchange step of the KV-range split without a collective on the data path (no counterpart in
+ * the reference, which has no multi-GPU decode).  Every rank owns a receive buffer of
+ * bkv_kv_exchange_bytes(world, rows) bytes - [2][world] records of rows*130 floats followed by
+ * [2][world] flag words - that all other ranks of the node map through CUDA IPC:
+ *   bkv_kv_exchange_alloc  allocates and zero-fills the buffer (set-up time: this is the one
+ *                          entry point of the library that allocates) and returns its 64-byte
+ *                          IPC handle, which the caller hands to the other ranks by any means;
+ *   bkv_kv_exchange_open / _close  map / unmap a peer's buffer from its handle;
+ *   bkv_kv_exchange_free   releases the own buffer (after every peer has closed it).
+ * bkv_kv_exchange_merge_sm100 is the per-step call, one kernel: it stores this rank's record
+ * (o | m | l as written by bkv_decode_range_stream_sm100 into one contiguous block) into slot
+ * `rank` of every peer's buffer with plain peer stores, publishes `step` in the peer's flag word,
+ * waits until the `world` flags of its own buffer show `step`, and merges the records by
+ * log-sum-exp into `out` ([rows][128]).  peer_buffers: host array of `world` device addresses,
+ * entry `rank` being the own buffer.  step: 1, 2, 3, ... the same sequence on every rank.
+ * The wait is bounded: after timeout_ns nanoseconds without the flags the kernel sets *status
+ * (device int, never cleared by the library) to 1, leaves `out` untouched and returns; nothing
+ * hangs when a peer is gone.  world <= 16.
+ */
+int64_t bkv_kv_exchange_bytes(int world, int64_t rows);
+int bkv_kv_exchange_alloc(int64_t bytes, void** buffer_out, unsigned char* handle64_out);
+int bkv_kv_exchange_open(const unsigned char* handle64, void** peer_out);
+int bkv_kv_exchange_close(void* peer);
+int bkv_kv_exchange_free(void* buffer);
+int bkv_kv_exchange_merge_sm100(const float* record, int64_t rows, const uint64_t* peer_buffers, int world,
+                                int rank, int step, int64_t timeout_ns, void* out, int out_dtype,
+                                float* out_f32, int* status, bkv_stream_t stream);
 
 /*
  * bkv_decode_sm100 for callers that cannot allocate device memory (no counterpart in

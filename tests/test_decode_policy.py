@@ -76,3 +76,25 @@ def test_reducer_names_of_the_reference_are_aliases():
         assert normalize_reduction_kind(name) == "lse_combine"
     with pytest.raises(ValueError, match="BEYOND_SM103_REDUCTION_KIND"):
         normalize_reduction_kind("tree")
+
+
+def test_device_status_is_turned_into_an_exception(monkeypatch):
+    """The error-reporting path on the host (no device involved): whatever the status entry point
+    reports is raised with its meaning; zero is silent."""
+    from beyond_kv_cache_b200 import _lib
+    from beyond_kv_cache_b200.quant.fa4_cute import beyond_mixed_decode_runtime as rt
+
+    reported = {"value": 0}
+
+    def fake_call(name, ref):
+        assert name == "bkv_decode_device_status"
+        ref._obj.value = reported["value"]
+
+    monkeypatch.setattr(_lib, "call", fake_call)
+    rt.check_device_status()
+    reported["value"] = 2
+    with pytest.raises(_lib.BkvError, match="bounded wait"):
+        rt.check_device_status()
+    reported["value"] = 3
+    with pytest.raises(_lib.BkvError, match="unexpected address"):
+        rt.check_device_status()

@@ -77,22 +77,59 @@ def test_register_backend_wires_registry_manager_and_spec(monkeypatch):
         def get_kv_cache_spec(self, vllm_config):
             return "stock"
 
+    from dataclasses import dataclass
+
+    @dataclass(frozen=True, kw_only=True)
+    class FullAttentionSpec:  # the fields the packed spec relies on
+        block_size: int
+        num_kv_heads: int
+        head_size: int
+        dtype: object = None
+
+    monkeypatch.setattr(packed_backend, "_VLLM_SPEC_CLASS", None)
     manager_map = {}
     for pkg in ("vllm", "vllm.v1", "vllm.v1.attention", "vllm.v1.attention.backends", "vllm.v1.core",
                 "vllm.model_executor", "vllm.model_executor.layers", "vllm.model_executor.layers.attention"):
         mod(pkg)
     mod("vllm.v1.attention.backends.registry", AttentionBackendEnum=SimpleNamespace(CUSTOM="CUSTOM"),
         register_backend=lambda slot, qualname: calls.update(slot=slot, qualname=qualname))
+    mod("vllm.v1.kv_cache_interface", FullAttentionSpec=FullAttentionSpec)
     mod("vllm.v1.core.single_type_kv_cache_manager", FullAttentionManager=FullAttentionManager, spec_manager_map=manager_map)
     mod("vllm.model_executor.layers.attention.attention", Attention=Attention)
     mod("vllm.v1.attention.backend", AttentionType=SimpleNamespace(DECODER="decoder"))
 
     assert registration.register_backend() is True
     assert calls["slot"] == "CUSTOM" and calls["qualname"].endswith("packed_backend.BeyondPackedBackend")
-    assert manager_map[packed_backend.BeyondPackedSpec] is FullAttentionManager
+    spec_cls = packed_backend.vllm_spec_class()
+    assert issubclass(spec_cls, FullAttentionSpec) and manager_map[spec_cls] is FullAttentionManager
     cfg = SimpleNamespace(cache_config=SimpleNamespace(block_size=16))
     spec = Attention("CUSTOM").get_kv_cache_spec(cfg)
-    assert isinstance(spec, packed_backend.BeyondPackedSpec) and spec.real_page_size_bytes == 16 * 8 * 160
+    assert isinstance(spec, spec_cls) and spec.real_page_size_bytes == 16 * 8 * 160
     assert Attention("FLASH_ATTN").get_kv_cache_spec(cfg) == "stock"
     patched = Attention.get_kv_cache_spec
     assert registration.register_backend() is True and Attention.get_kv_cache_spec is patched  # idempotent
+
+
+def test_packed_spec_against_the_installed_vllm(monkeypatch):
+    """Against the vLLM that is actually installed (skipped when it does not import here): the
+    packed spec is a KVCacheSpec that vLLM's page-size arithmetic accepts, its page is the packed
+    page, and the registry has the CUSTOM slot the backend registers into."""
+    pytest.importorskip("vllm")
+    try:
+        from vllm.v1.attention.backends.registry import AttentionBackendEnum
+        from vllm.v1.kv_cache_interface import FullAttentionSpec, KVCacheSpec
+    except Exception as exc:  # an installed vLLM whose pieces need a GPU driver to import
+        pytest.skip(f"vLLM interfaces not importable here: {exc!r}")
+    import torch
+
+    monkeypatch.setattr(packed_backend, "_VLLM_SPEC_CLASS", None)
+    spec_cls = packed_backend.vllm_spec_class()
+    assert issubclass(spec_cls, FullAttentionSpec) and issubclass(spec_cls, KVCacheSpec)
+    spec = spec_cls(block_size=16, num_kv_heads=8, head_size=128, dtype=torch.int32)
+    assert spec.real_page_size_bytes == 5120 * 4 == packed_backend.BeyondPackedSpec(16, 8, 128).real_page_size_bytes
+    assert spec.page_size_bytes == 5120 * 4  # what the allocator sizes the pool with
+    big = spec_cls(block_size=128, num_kv_heads=8, head_size=128, dtype=torch.int32)
+    assert big.page_size_bytes == 8 * 5120 * 4
+    assert hasattr(AttentionBackendEnum, "CUSTOM")
+    shape = packed_backend.BeyondPackedBackend.get_kv_cache_shape(7, 16, 8, 128)
+    assert shape[0] * shape[1] * 4 == 7 * spec.page_size_bytes
