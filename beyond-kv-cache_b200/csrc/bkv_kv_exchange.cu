@@ -6,7 +6,7 @@
 // each, mapped into all the others through CUDA IPC: [2 parities][world][record] floats followed
 // by [2][world] flag words.  ONE kernel per step then
 //   1. pushes this rank's record into slot `rank` of every peer's buffer with plain peer stores
-//      (CTA r writes to rank r; no multicast), makes it visible system-wide and publishes the
+//      (CTA r writes to rank r, one peer at a time), makes it visible system-wide and publishes the
 //      step number in the peer's flag word;
 //   2. waits - with a time limit - until all `world` flags of its own buffer show this step;
 //   3. merges the `world` records by log-sum-exp into the attention output, as
