@@ -636,6 +636,19 @@ def measure_reference_kernel(args, dev, page: int = 128):
             our_step()
             torch.cuda.synchronize()
             record["reference"]["max_abs_vs_this_library"] = float((theirs.float() - ours.float()).abs().max().item())
+            # both against the float64 oracle over the same pages, rounded to the output type (request 0)
+            import numpy as np
+
+            import oracle
+
+            ids = block_table[0, :pages_per_seq].long()
+            want = oracle.decode_attention(q[0:1].float().cpu().numpy(), cache[ids].cpu().numpy(), oracle.PageGeometry(page, HEADS_KV),
+                                           np.arange(pages_per_seq, dtype=np.int32)[None, :], [ctx], levels_k=lk.float().cpu().numpy(),
+                                           levels_v=lv.float().cpu().numpy(), softmax_scale=scale, stat="bf16")
+            want16 = torch.from_numpy(want).to(q.dtype).float().numpy()
+            record["reference"]["bf16_output_max_abs_vs_rounded_oracle"] = float(np.abs(theirs[0:1].float().cpu().numpy() - want16).max())
+            record["this_library_bf16_output_max_abs_vs_rounded_oracle"] = float(np.abs(ours[0:1].float().cpu().numpy() - want16).max())
+            record["oracle_max_abs_value"] = float(np.abs(want16).max())
             record["reference"]["us"] = timed(ref_step, min(args.steps, 200))
     except BaseException as exc:  # noqa: BLE001  (DSL / compiler / launch refusals are the record)
         import traceback

@@ -430,9 +430,9 @@ __global__ void __maxnreg__(max_regs_for(NW))
   // ---- per-lane roles (see the file comment) ----------------------------------------------
   const int ksel = tig >> 1, khalf = tig & 1;     // QK: this lane's k-slots carry half khalf of group 2*ksel+P
   const int tq0 = gid;                            // QK rows gid / gid+8 carry tokens gid / gid+8
-  const uint32_t kc_off0 = swz(kSwKCode + tq0 * 64 + (2 * ksel) * 16) + khalf * 8;      // pair 0; +512: row gid+8
-  const uint32_t kc_off1 = swz(kSwKCode + tq0 * 64 + (2 * ksel + 1) * 16) + khalf * 8;  // pair 1
-  const uint32_t ks_off0 = swz(kSwKStat + tq0 * 16), ks_off1 = swz(kSwKStat + (tq0 + 8) * 16);
+  uint32_t kc_off0 = swz(kSwKCode + tq0 * 64 + (2 * ksel) * 16) + khalf * 8;      // pair 0; +512: row gid+8
+  uint32_t kc_off1 = swz(kSwKCode + tq0 * 64 + (2 * ksel + 1) * 16) + khalf * 8;  // pair 1
+  uint32_t ks_off0 = swz(kSwKStat + tq0 * 16), ks_off1 = swz(kSwKStat + (tq0 + 8) * 16);
   const int vsel = gid >> 2, vu = gid & 3;        // PV: rows gid/gid+8 are dims 8*vu+2i(+1) of group 2*vsel+P
   const int hcol = gid >> 1, gsel = gid & 1;      // B column gid: query head hcol, group 2*gsel+P
   // PV k-slots 2tig, 2tig+1 (+8) carry tokens tig, tig+4 (+8): four consecutive tokens per load
@@ -443,16 +443,24 @@ __global__ void __maxnreg__(max_regs_for(NW))
     for (int P = 0; P < 2; ++P) vc_off[e][P] = swz(kSwVCode + (tig + 4 * e) * 64 + (2 * vsel + P) * 16) + vu * 4;
   // V statistic word of (group 2*gsel+P, token tig+4e+8o): +64 for pair 1, +32 for o = 0 (the
   // swizzle of this part flips the bit that o sets)
-  const uint32_t vs_off0 = swz(kSwVStat + (2 * gsel) * 64 + (tig + 8) * 4);
-  const uint32_t vs_off1 = swz(kSwVStat + (2 * gsel) * 64 + (tig + 4 + 8) * 4);
-  const uint32_t klane0 = kLutAddr | (lane * 4), klane1 = klane0 + kLutBlock;
-  const uint32_t vlane0 = kLutAddr | (lane * 4 + 128), vlane1 = vlane0 + kLutBlock;
+  uint32_t vs_off0 = swz(kSwVStat + (2 * gsel) * 64 + (tig + 8) * 4);
+  uint32_t vs_off1 = swz(kSwVStat + (2 * gsel) * 64 + (tig + 4 + 8) * 4);
+  uint32_t klane0 = kLutAddr | (lane * 4), klane1 = klane0 + kLutBlock;
+  uint32_t vlane0 = kLutAddr | (lane * 4 + 128), vlane1 = vlane0 + kLutBlock;
   // probabilities travel from the QK layout (token by gid, head by tig) to the PV layout (token by tig, head by gid)
   const int src_lane0 = tig * 4 + hcol;        // row holding tokens tig, tig+8     (k-slots 2tig, 2tig+8)
   const int src_lane1 = (tig + 4) * 4 + hcol;  // row holding tokens tig+4, tig+12  (k-slots 2tig+1, 2tig+9)
+  // These per-lane offsets are used by every tile.  Left as plain expressions of the lane index
+  // the compiler recomputes them inside the tile loop (dozens of integer instructions per tile);
+  // passed through an empty asm statement they are opaque values that stay in registers.
+  keep_in_register(kc_off0), keep_in_register(kc_off1), keep_in_register(ks_off0), keep_in_register(ks_off1);
+  keep_in_register(vc_off[0][0]), keep_in_register(vc_off[0][1]), keep_in_register(vc_off[1][0]), keep_in_register(vc_off[1][1]);
+  keep_in_register(vs_off0), keep_in_register(vs_off1);
+  keep_in_register(klane0), keep_in_register(klane1), keep_in_register(vlane0), keep_in_register(vlane1);
 
   // ---- ring state of this warp: tile number g of its lifetime lives in stage g % STAGES ----
-  const uint32_t ring_base = R::base(warp);
+  uint32_t ring_base = R::base(warp);
+  keep_in_register(ring_base);
   const uint32_t bar_base = kFullBar + 8 * (warp * STAGES);
   int s = 0;           // stage of the next tile to consume
   uint32_t phase = 0;  // parity of that stage's current use
@@ -462,7 +470,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
   uint32_t table_parity = 0;
 
   const PageGeom geo = make_geom(BS, p.heads_kv);
-  const int64_t page_bytes = p.page_stride * 4;
+  const uint32_t page_bytes = static_cast<uint32_t>(p.page_stride * 4);  // (a page is far below 4 GiB)
   const uint32_t num_pages_u = static_cast<uint32_t>(p.num_pages);
 
   auto wait_full = [&](uint32_t bar, uint32_t parity) -> bool {  // false: the bounded wait gave up
@@ -570,7 +578,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
       const uint32_t dst = ring_base + stage * kSlotBytes;
       if (LOADER == 1) {
         if (!bad) {
-          const char* const page = reinterpret_cast<const char*>(p.cache) + phys * page_bytes;
+          const char* const page = reinterpret_cast<const char*>(p.cache) + static_cast<uint64_t>(phys) * page_bytes;
           const char* const kp = page + (ld_kcode + sub * 1024);
           const char* const vp = page + (ld_vcode + sub * 1024);
           const uint32_t dl = dst + ld_code_dst;
@@ -728,14 +736,17 @@ __global__ void __maxnreg__(max_regs_for(NW))
       }
       // ------------------------------ online softmax over the tile(s) -------------------------
       // (the scores are still un-scaled; the scale is positive, so the maximum commutes with it)
+      // Most tiles leave the running maximum alone: every lane tests its own scores against it,
+      // and only when some lane of the warp is beyond the threshold are the maxima of the heads
+      // reduced over the lanes (the same decision per head as reducing first).
       float tmax = fmaxf(sc[0][0], sc[0][1]);
       if (NT == 2) tmax = fmaxf(tmax, fmaxf(sc[NT - 1][0], sc[NT - 1][1]));
-      tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 4));
-      tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 8));
-      tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 16));
-      tmax *= p.scale_log2;
-      const bool need = tmax > m_used + kRescaleThreshold;
-      if (__any_sync(kFull, need)) {
+      if (__any_sync(kFull, tmax * p.scale_log2 > m_used + kRescaleThreshold)) {
+        tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 4));
+        tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 8));
+        tmax = fmaxf(tmax, __shfl_xor_sync(kFull, tmax, 16));
+        tmax *= p.scale_log2;
+        const bool need = tmax > m_used + kRescaleThreshold;
         const float m_new = need ? tmax : m_used;
         const float corr = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_used - m_new);
         m_used = m_new;
@@ -901,11 +912,16 @@ __global__ void __maxnreg__(max_regs_for(NW))
         const int cnt = nb <= 4 ? 1 : min(PAIR, kend - k);
         const int sB = s + 1 == STAGES ? 0 : s + 1;
         const uint32_t phaseB = s + 1 == STAGES ? phase ^ 1u : phase;
-        auto wait_tile = [&](int ahead, int stage, uint32_t parity) {  // tile n_done + ahead of this warp
-          if (n_done + ahead >= n_issued) return;
+        auto wait_tile = [&](auto ahead_tag, int stage, uint32_t parity) {  // tile n_done + ahead of this warp
+          constexpr int kAhead = decltype(ahead_tag)::value;
+          const int in_flight = n_issued - n_done;  // tiles issued and not yet consumed
+          if (in_flight <= kAhead) return;
           if (LOADER == 1) {
-            cp_async_wait_pending(n_issued - n_done - ahead - 1);  // this thread's pieces of the tile ...
-            __syncwarp();                                           // ... and every other lane's
+            // this thread's pieces of the tile: with a full ring the newer STAGES - 1 - kAhead groups may
+            // still be under way; near the end of a run simply everything is awaited ...
+            if (in_flight == STAGES) cp_async_wait_group<STAGES - 1 - kAhead>();
+            else cp_async_wait_group<0>();
+            __syncwarp();  // ... and every other lane's
           } else if (!wait_full(bar_base + 8 * stage, parity)) {
             dead = true;
           }
@@ -915,13 +931,13 @@ __global__ void __maxnreg__(max_regs_for(NW))
           if (LOADER != 1) fence_proxy_async();  // reads of the generic proxy before writes of the async proxy
           if (run_done + ahead + STAGES < total) issue(run_done + ahead + STAGES, stage);
         };
-        wait_tile(0, s, phase);
+        wait_tile(std::integral_constant<int, 0>{}, s, phase);
         if (dead) break;
         const int rem = ntok - kTile * k;
         const int nvA = (bad_mask >> s) & 1 ? 0 : min(kTile, rem);
         const int nvB = cnt == 2 ? ((bad_mask >> sB) & 1 ? 0 : min(kTile, rem - kTile)) : 0;
         const uint32_t sbA = ring_base + s * kSlotBytes, sbB = ring_base + sB * kSlotBytes;
-        auto wait_second = [&] { wait_tile(1, sB, phaseB); };
+        auto wait_second = [&] { wait_tile(std::integral_constant<int, 1>{}, sB, phaseB); };
         auto refill_tile = [&](int t) { refill(t, t ? sB : s); };
         if (cnt == 2) {
           if (nvA == kTile && nvB == kTile) {
@@ -1494,6 +1510,7 @@ int launch_decode_stream(const DecodeParams& p, void* ws, int64_t ws_bytes, cons
   const int r = p.block_size / kTile;
   if (p.block_size % kTile != 0 || (r & (r - 1)) != 0 || p.block_size > 1024) return BKV_ERR_UNSUPPORTED;
   if ((p.page_stride * 4) % 16 != 0 || !aligned16(p.cache)) return BKV_ERR_UNSUPPORTED;
+  if (p.page_stride * 4 >= (1ll << 32)) return BKV_ERR_UNSUPPORTED;  // the kernel multiplies page ids by a 32-bit stride
   if (p.token_lo % p.block_size != 0) return BKV_ERR_UNSUPPORTED;
   if (p.batch > kMaxBatchPlanned || p.num_pages > (1ll << kMaxPagesLog2)) return BKV_ERR_UNSUPPORTED;
   // the byte tables hold fp16 levels: 16-bit level tables convert exactly, float32 ones would be rounded

@@ -135,6 +135,9 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
   asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
   return r;
 }
+// Makes a value opaque to the optimiser at this point: it is neither recomputed from its
+// definition later nor folded into the expressions that use it; it simply lives in a register.
+__device__ __forceinline__ void keep_in_register(uint32_t& v) { asm volatile("" : "+r"(v)); }
 // Table look-up: the address is complete, no base is added.  Not volatile: the table is
 // constant once built, so the compiler may schedule these freely.
 __device__ __forceinline__ uint32_t lut_load(uint32_t addr) {
