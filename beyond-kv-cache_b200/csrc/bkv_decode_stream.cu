@@ -907,7 +907,34 @@ __global__ void __maxnreg__(max_regs_for(NW))
                                (static_cast<int64_t>(b + 1) * p.q_batch_stride + static_cast<int64_t>(hq0) * kHeadDim) * esize;
         if (lane * 128 < nh * kHeadDim * esize) asm volatile("prefetch.global.L2 [%0];" ::"l"(nq + lane * 128));
       }
-      for (int k = k0; k < kend;) {
+      int k = k0;
+      // ---- steady state: pairs of complete tiles with the ring full and a refill behind each ----
+      // (no per-tile case analysis: the conditions below are checked once per pair, and everything
+      // that fails them - the ends of a run, ragged tails, unmapped pages, short requests - takes
+      // the general loop further down, which computes the same values for complete tiles)
+      if (LOADER == 1 && PAIR == 2 && nb > 4) {
+        const int k_fast = min(kend, ntok / kTile);  // complete tiles of this part
+        while (k + 2 <= k_fast && run_done + 2 + STAGES <= total && bad_mask == 0 && n_issued - n_done == STAGES) {
+          const int sB = s + 1 == STAGES ? 0 : s + 1;
+          cp_async_wait_group<STAGES - 1>();
+          __syncwarp();
+          process(std::integral_constant<int, 2>{}, std::false_type{}, ring_base + s * kSlotBytes, ring_base + sB * kSlotBytes,
+                  kTile, kTile,
+                  [&] {
+                    cp_async_wait_group<STAGES - 2>();
+                    __syncwarp();
+                  },
+                  [&](int t) {
+                    __syncwarp();
+                    issue(run_done + t + STAGES, t ? sB : s);
+                  });
+          k += 2;
+          run_done += 2;
+          n_done += 2;
+          s = sB + 1 == STAGES ? 0 : sB + 1;
+        }
+      }
+      for (; k < kend;) {
         // a request of a few tiles is processed one tile at a time, i.e. by the precise form
         const int cnt = nb <= 4 ? 1 : min(PAIR, kend - k);
         const int sB = s + 1 == STAGES ? 0 : s + 1;
@@ -940,7 +967,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
         auto wait_second = [&] { wait_tile(std::integral_constant<int, 1>{}, sB, phaseB); };
         auto refill_tile = [&](int t) { refill(t, t ? sB : s); };
         if (cnt == 2) {
-          if (nvA == kTile && nvB == kTile) {
+          if (LOADER != 1 && nvA == kTile && nvB == kTile) {
             process(std::integral_constant<int, 2>{}, std::false_type{}, sbA, sbB, nvA, nvB, wait_second, refill_tile);
           } else if (nvA > 0 || nvB > 0) {
             process(std::integral_constant<int, 2>{}, std::true_type{}, sbA, sbB, nvA, nvB, wait_second, refill_tile);
