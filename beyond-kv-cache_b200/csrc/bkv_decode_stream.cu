@@ -516,9 +516,9 @@ __global__ void __maxnreg__(max_regs_for(NW))
     // cp.async loader: lane l moves the l-th 16 bytes of each 512-byte half of the K and V
     // codes (tokens 0-7 / 8-15); lanes 0-15 move the K statistics, lanes 16-31 the V statistics
     const uint32_t code_head = head * (BS * kWordsPerHead) * 4;
-    const uint32_t ld_kcode = geo.k_code_off * 4 + code_head + lane * 16;
-    const uint32_t ld_vcode = geo.v_code_off * 4 + code_head + lane * 16;
-    const uint32_t ld_code_dst = swz(lane * 16);  // the swizzle repeats every 512 bytes
+    uint32_t ld_kcode = geo.k_code_off * 4 + code_head + lane * 16;
+    uint32_t ld_vcode = geo.v_code_off * 4 + code_head + lane * 16;
+    uint32_t ld_code_dst = swz(lane * 16);  // the swizzle repeats every 512 bytes
     uint32_t ld_stat_src, ld_stat_dst, ld_stat_sub;
     if (lane < 16) {
       ld_stat_src = (geo.k_stat_off + head * (BS * 4)) * 4 + lane * 16;
@@ -530,6 +530,8 @@ __global__ void __maxnreg__(max_regs_for(NW))
       ld_stat_dst = swz(kSwVStat + g * 64 + c * 16);
       ld_stat_sub = 64;
     }
+    keep_in_register(ld_kcode), keep_in_register(ld_vcode), keep_in_register(ld_code_dst);
+    keep_in_register(ld_stat_src), keep_in_register(ld_stat_dst), keep_in_register(ld_stat_sub);
     // tensor-copy loader: 64-byte rows of the code and the statistic part inside each half of a page
     const int row_code = code_head >> 6;
     const int row_stat = ((geo.k_stat_off + head * (BS * 4)) * 4) >> 6;
@@ -654,7 +656,8 @@ __global__ void __maxnreg__(max_regs_for(NW))
 
     // ---- attention state of the request being streamed ------------------------------------
     uint32_t qb[2][4][2];  // B operand of QK: q of head hcol as fp16 (exact for 16-bit queries)
-    float qs[4];           // sum over the dims of group g of the fp16 q of head tig
+    float qs[4];           // sum over the dims of group g of the fp16 q of head tig (bf16 statistics)
+    uint32_t qmin_b[2];    // fp16 statistics: B operand that multiplies the K minima by those sums
     float oacc[2][4][4], cmin[2][4];
     float m_used = -CUDART_INF_F, l_run = 0.f;  // head tig
 
@@ -714,19 +717,38 @@ __global__ void __maxnreg__(max_regs_for(NW))
       float sc[NT][2];
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
+        // statistic words (scale low, minimum high) of groups 0..3 for tokens gid (s0) and gid+8 (s1)
+        const uint4 s0 = ring_load128i<0>(sb[t] + ks_off0), s1 = ring_load128i<0>(sb[t] + ks_off1);
+        float mm[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!STAT_BF16) {
+          // fp16 minima go to the tensor cores as they are: sum_g min[token][g] * qsum[g][head] is one
+          // more MMA.  A = the high halves of the words (in every lane: groups 0,1 in k-slots 2tig..,
+          // groups 2,3 in k-slots 2tig+8..; B is zero outside the k rows of lane 0), B = the sums as
+          // (high, low) fp16 parts in columns 2*head, 2*head+1; the two columns are added below.
+          mma16816_zero(mm, __byte_perm(s0.x, s0.y, 0x7632), __byte_perm(s1.x, s1.y, 0x7632), __byte_perm(s0.z, s0.w, 0x7632),
+                        __byte_perm(s1.z, s1.w, 0x7632), qmin_b[0], qmin_b[1]);
+        }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          const uint4 st = ring_load128i<0>(sb[t] + (r ? ks_off1 : ks_off0));  // groups 0..3
-          const float2 g0 = stat_word_to_f32<STAT_BF16>(st.x), g1 = stat_word_to_f32<STAT_BF16>(st.y);
-          const float2 g2 = stat_word_to_f32<STAT_BF16>(st.z), g3 = stat_word_to_f32<STAT_BF16>(st.w);
-          float u = g0.x * sacc[t][0][2 * r];       // column 2tig: group P, column 2tig+1: group P+2
-          float v = g1.x * sacc[t][1][2 * r];
-          u = fmaf(g2.x, sacc[t][0][2 * r + 1], u);
-          v = fmaf(g3.x, sacc[t][1][2 * r + 1], v);
-          u = fmaf(g0.y, qs[0], u);
-          v = fmaf(g1.y, qs[1], v);
-          u = fmaf(g2.y, qs[2], u);
-          v = fmaf(g3.y, qs[3], v);
+          const uint4 st = r ? s1 : s0;
+          float u, v;  // column 2tig of an accumulator: group P, column 2tig+1: group P+2
+          if (!STAT_BF16) {
+            u = fmaf(f16_bits_to_f32(st.x & 0xFFFFu), sacc[t][0][2 * r], mm[2 * r]);
+            v = fmaf(f16_bits_to_f32(st.y & 0xFFFFu), sacc[t][1][2 * r], mm[2 * r + 1]);
+            u = fmaf(f16_bits_to_f32(st.z & 0xFFFFu), sacc[t][0][2 * r + 1], u);
+            v = fmaf(f16_bits_to_f32(st.w & 0xFFFFu), sacc[t][1][2 * r + 1], v);
+          } else {
+            const float2 g0 = stat_word_to_f32<true>(st.x), g1 = stat_word_to_f32<true>(st.y);
+            const float2 g2 = stat_word_to_f32<true>(st.z), g3 = stat_word_to_f32<true>(st.w);
+            u = g0.x * sacc[t][0][2 * r];
+            v = g1.x * sacc[t][1][2 * r];
+            u = fmaf(g2.x, sacc[t][0][2 * r + 1], u);
+            v = fmaf(g3.x, sacc[t][1][2 * r + 1], v);
+            u = fmaf(g0.y, qs[0], u);
+            v = fmaf(g1.y, qs[1], v);
+            u = fmaf(g2.y, qs[2], u);
+            v = fmaf(g3.y, qs[3], v);
+          }
           float x = u + v;
           if (PARTIAL) {  // behind the end of the sequence (statistics may be NaN)
             if (tq0 + 8 * r >= nv[t]) x = -CUDART_INF_F;
@@ -887,6 +909,19 @@ __global__ void __maxnreg__(max_regs_for(NW))
           qsum[P] += __shfl_xor_sync(kFull, qsum[P], 1);  // both halves of the group
 #pragma unroll
           for (int e = 0; e < 2; ++e) qs[2 * e + P] = __shfl_sync(kFull, qsum[P], (2 * tig) * 4 + 2 * e);
+        }
+        if (!STAT_BF16) {
+          // this lane holds the sums of groups 2*ksel, 2*ksel+1 of head hcol; lane (gid, 0) gathers all four
+          const float g2s = __shfl_sync(kFull, qsum[0], gid * 4 + 2), g3s = __shfl_sync(kFull, qsum[1], gid * 4 + 2);
+          const float four[4] = {qsum[0], qsum[1], g2s, g3s};
+          float part[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const float hi = __half2float(__float2half_rn(four[g]));
+            part[g] = (gid & 1) ? four[g] - hi : hi;  // column 2*head: high part, 2*head+1: what it dropped
+          }
+          qmin_b[0] = tig == 0 ? pack_half2(part[0], part[1]) : 0u;
+          qmin_b[1] = tig == 0 ? pack_half2(part[2], part[3]) : 0u;
         }
       }
 #pragma unroll
