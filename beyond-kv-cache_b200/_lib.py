@@ -18,7 +18,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libbkv_sm100.so")
 
 BKV_F16, BKV_BF16, BKV_F32 = 0, 1, 2
 LAYOUT_HEAD_WORD_TOKEN, LAYOUT_HND_TOKEN_WORD = 1, 2
-FLAG_PDL_TRIGGER, FLAG_PDL_WAIT, FLAG_LINEAR_SEARCH, FLAG_KLEVELS_LANE_MAJOR = 1, 2, 4, 8
+FLAG_PDL_TRIGGER, FLAG_PDL_WAIT, FLAG_LINEAR_SEARCH, FLAG_KLEVELS_LANE_MAJOR, FLAG_BINNED_TABLES = 1, 2, 4, 8, 16
 ERR_ARG, ERR_UNSUPPORTED, ERR_ALIGN, ERR_CUDA, ERR_LIMIT = -1, -2, -3, -4, -5
 
 _c = ctypes

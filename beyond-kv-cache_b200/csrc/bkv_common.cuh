@@ -73,6 +73,9 @@ __device__ __forceinline__ float load_table_f32(const void* base, int idx, int d
 __device__ __forceinline__ float shared_f32(uint32_t addr) {
   return *static_cast<const float*>(__cvta_shared_to_generic(addr));
 }
+__device__ __forceinline__ uint32_t shared_u32(uint32_t addr) {
+  return *static_cast<const uint32_t*>(__cvta_shared_to_generic(addr));
+}
 
 // ---- PTX wrappers -------------------------------------------------------------
 __device__ __forceinline__ void pdl_launch_dependents() {

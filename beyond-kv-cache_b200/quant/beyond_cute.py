@@ -270,22 +270,44 @@ def _stat_dtype_from_model_dtype(dtype: torch.dtype) -> torch.dtype:
 
 
 # --------------------------------------------------------------------------- helpers
-def _tables_sorted(thr: torch.Tensor) -> bool:
-    """True when every threshold table is non-decreasing (binary search is then
-    identical to the reference's count).  The answer is kept on the tensor object itself,
-    tagged with the tensor version it was computed for, so it can never be inherited by
-    another table that the allocator later places at the same address.  Finding it out costs
-    one device read; during stream capture an unclassified table is treated as unsorted
-    (the counting search is always right, only slower)."""
+def _table_class(thr: torch.Tensor) -> tuple:
+    """(sorted, binned) for a threshold tensor.
+
+    sorted: every table is non-decreasing (the binary search is then identical to the reference's
+    count).  binned: in addition every threshold is positive with the low four bits of its float32
+    pattern clear (any 16-bit value) and every interval [e/512, (e+1)/512), e = 0..511, holds at
+    most one threshold of a table, which lets large writes replace the search by one indexed
+    look-up (tables that obey the 2^-9 minimum-gap rule of the reference's
+    ``quantization/table_precision.py:19-24`` are of this kind).  The answer is kept on the tensor
+    object itself, tagged with the tensor version it was computed for, so it can never be
+    inherited by another table that the allocator later places at the same address.  Finding it
+    out costs one device read; during stream capture an unclassified table is treated as
+    unsorted and not binned (the counting search is always right, only slower)."""
     held = getattr(thr, "_bkv_sorted", None)
     if held is not None and held[0] == thr._version:
         return held[1]
     if thr.is_cuda and torch.cuda.is_current_stream_capturing():
-        return False
-    t = thr.float()
-    known = bool((t[..., 1:] >= t[..., :-1]).all().item())
+        return (False, False)
+    t = thr.float().reshape(-1, thr.shape[-1])
+    is_sorted = t[:, 1:] >= t[:, :-1]
+    # interval index of every threshold that can matter (those in [0, 1)); NaNs never count
+    inside = (t >= 0) & (t < 1)
+    bins = torch.where(inside, torch.floor(t * 512.0), torch.arange(t.shape[-1], device=t.device, dtype=t.dtype) - 1000.0)
+    ordered = torch.sort(bins, dim=-1).values
+    distinct = ordered[:, 1:] != ordered[:, :-1]
+    plain = (t > 0).all() & ((t.contiguous().view(torch.int32) & 15) == 0).all()
+    answers = torch.stack([is_sorted.all(), distinct.all() & plain]).tolist()
+    known = (bool(answers[0]), bool(answers[0]) and bool(answers[1]))
     thr._bkv_sorted = (thr._version, known)
     return known
+
+
+def _tables_sorted(thr: torch.Tensor) -> bool:
+    return _table_class(thr)[0]
+
+
+def _tables_binned(thr: torch.Tensor) -> bool:
+    return _table_class(thr)[1]
 
 
 def classify_tables(*thresholds: torch.Tensor) -> None:
@@ -403,6 +425,8 @@ def write_tokens_to_paged_cache(
     flags = _lib.FLAG_PDL_TRIGGER if signal_pdl_dependents else 0
     if not (_tables_sorted(thr_k) and _tables_sorted(thr_v)):
         flags |= _lib.FLAG_LINEAR_SEARCH
+    elif _tables_binned(thr_k) and _tables_binned(thr_v):
+        flags |= _lib.FLAG_BINNED_TABLES
     dq = k_dq_out is not None
     _lib.call(
         "bkv_encode_sm100",

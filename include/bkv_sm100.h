@@ -54,6 +54,14 @@ extern "C" {
                                       read before the wait and must come from older launches */
 #define BKV_FLAG_LINEAR_SEARCH 0x4 /* encode: count thresholds linearly (unsorted tables) */
 #define BKV_FLAG_KLEVELS_LANE_MAJOR 0x8 /* decode: K levels given as (Hkv,16,4)      */
+#define BKV_FLAG_BINNED_TABLES 0x10 /* encode: the caller has checked, for both threshold tensors,
+                                      that every table is ascending, every threshold positive with
+                                      the low four bits of its float32 pattern clear (any 16-bit
+                                      value), and that every interval [e/512, (e+1)/512),
+                                      e = 0..511, holds at most one threshold of a table (true
+                                      when neighbouring thresholds are 2^-9 or more apart): large
+                                      writes then replace the search by one indexed look-up.  A
+                                      wrong claim gives wrong codes, never a bad access.       */
 
 typedef void* bkv_stream_t; /* a cudaStream_t / CUstream */
 

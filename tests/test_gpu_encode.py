@@ -139,6 +139,96 @@ def test_writer_matches_oracle_random(tokens, heads, shared, kind):
     assert np.array_equal(cache.cpu().numpy(), expect)
 
 
+def _threshold_hitting_rows(rng, tokens, heads, thr16):
+    """float32 rows whose normalised values land exactly on thresholds and interval borders: every
+    group holds 0 and 1 (so scale = 1, min = 0 and x_norm = x), the rest are thresholds of the
+    group's own table, their fp16 neighbours, and multiples of 2^-9 with their float32 neighbours."""
+    x = np.empty((tokens, heads, 128), dtype=np.float32)
+    thr = thr16.float().numpy().reshape(heads, 4, 15)
+    for h in range(heads):
+        for g in range(4):
+            t = thr[h, g]
+            neighbours = np.concatenate([t, np.nextafter(t.astype(np.float16), np.float16(0)).astype(np.float32),
+                                         np.nextafter(t.astype(np.float16), np.float16(1)).astype(np.float32)])
+            borders = rng.integers(0, 513, 64).astype(np.float32) / 512.0
+            borders = np.concatenate([borders, np.nextafter(borders, np.float32(0)), np.nextafter(borders, np.float32(1))])
+            pool = np.clip(np.concatenate([neighbours, borders]), 0.0, 1.0).astype(np.float32)
+            x[:, h, 32 * g : 32 * g + 32] = rng.choice(pool, (tokens, 32))
+            x[:, h, 32 * g] = 0.0
+            x[:, h, 32 * g + 1] = 1.0
+    return x
+
+
+@pytest.mark.parametrize("kind,table_dtype,heads,shared", [("f16", torch.float16, 8, False), ("bf16", torch.float16, 3, False),
+                                                        ("f16", torch.float32, 8, False), ("bf16", torch.float16, 8, True)])
+def test_large_writes_with_classified_tables(kind, table_dtype, heads, shared):
+    """Writes large enough for the indexed look-up (tables with at most one threshold per interval
+    of 2^-9): page bytes and the in-place reconstruction against the oracle, on random rows and on
+    rows whose normalised values sit exactly on thresholds and interval borders."""
+    from beyond_kv_cache_b200.quant.beyond_cute import _tables_binned
+
+    rng = np.random.default_rng(41 + heads)
+    tokens, bs = 6000, 16
+    dt = KIND_TO_DTYPE[kind]
+    lk, tk, lv, tv = tables(heads, 9, per_group=not shared)
+    if shared:
+        lk, tk, lv, tv = lk[:1].reshape(16), tk[:1].reshape(15), lv[:1].reshape(16), tv[:1].reshape(15)
+        tk_all, tv_all = tk.repeat(heads * 4, 1), tv.repeat(heads * 4, 1)
+    else:
+        tk_all, tv_all = tk, tv
+    k32 = rng.standard_normal((tokens, heads, 128)).astype(np.float32)
+    v32 = _threshold_hitting_rows(rng, tokens, heads, tv_all)
+    k32[::3] = _threshold_hitting_rows(rng, len(k32[::3]), heads, tk_all)
+    k = torch.from_numpy(k32).to(dt)
+    v = torch.from_numpy(v32).to(dt)
+    pages = tokens // bs + 5
+    geo = oracle.PageGeometry(bs, heads, 128)
+    seed_pages = rng.integers(-(2**31), 2**31, (pages, geo.block_i32)).astype(np.int32)
+    slots = rng.permutation(pages * bs)[:tokens].astype(np.int64)
+    slots[::29] = -1
+    expect = seed_pages.copy()
+    oracle.write_pages(expect, geo, slots, k.float().numpy(), v.float().numpy(), thresholds_k=tk.float().numpy(),
+                       thresholds_v=tv.float().numpy(), stat=kind)
+    tabs = [t.to(table_dtype).to(DEV) for t in (lk, tk, lv, tv)]
+    assert _tables_binned(tabs[1]) and _tables_binned(tabs[3])
+    cache = torch.from_numpy(seed_pages).to(DEV)
+    kd, vd = k.to(DEV), v.to(DEV)
+    write_tokens_to_paged_cache(cache, PagedLayout.build_hnd(bs, heads, 128, 4, 32, 32), None, torch.from_numpy(slots).to(DEV), kd, vd,
+                                q_points_k=tabs[0], q_points_v=tabs[2], thresholds_k=tabs[1], thresholds_v=tabs[3],
+                                k_dq_out=kd, v_dq_out=vd, require_fast=True)
+    assert np.array_equal(cache.cpu().numpy(), expect)
+    for got, src, lvl, thr in ((kd, k, lk, tk), (vd, v, lv, tv)):
+        enc = oracle.encode_groups(src.float().numpy(), thr.float().numpy(), stat=kind)
+        want = oracle.decode_groups(enc["codes"], lvl.float().numpy(), enc["scale_bits"], enc["mn_bits"], stat=kind)
+        assert np.array_equal(bits16(got), bits16(torch.from_numpy(want).to(dt)))  # slot -1 rows too
+
+
+def test_tables_with_two_thresholds_in_one_interval_keep_the_search():
+    from beyond_kv_cache_b200.quant.beyond_cute import _tables_binned, _tables_sorted
+
+    heads, tokens, bs = 2, 5000, 16
+    lk, tk, lv, tv = tables(heads, 3)
+    tk = tk.clone()
+    tk[:, 7] = tk[:, 6] + 2.0**-11  # sorted, but two thresholds 2^-11 apart
+    assert _tables_sorted(tk.to(DEV)) and not _tables_binned(tk.to(DEV))
+    negative = tv.clone()
+    negative[:, 0] = -0.25
+    assert not _tables_binned(negative.to(DEV))
+    rng = np.random.default_rng(5)
+    k = torch.from_numpy(rng.standard_normal((tokens, heads, 128)).astype(np.float32)).to(torch.float16)
+    geo = oracle.PageGeometry(bs, heads, 128)
+    pages = tokens // bs + 1
+    expect = np.zeros((pages, geo.block_i32), dtype=np.int32)
+    slots = np.arange(tokens, dtype=np.int64)
+    oracle.write_pages(expect, geo, slots, k.float().numpy(), k.float().numpy(), thresholds_k=tk.float().numpy(),
+                       thresholds_v=tv.float().numpy())
+    cache = torch.zeros((pages, geo.block_i32), dtype=torch.int32, device=DEV)
+    write_tokens_to_paged_cache(cache, PagedLayout.build_hnd(bs, heads, 128, 4, 32, 32), None, torch.from_numpy(slots).to(DEV),
+                                k.to(DEV), k.to(DEV), q_points_k=lk.to(DEV), q_points_v=lv.to(DEV), thresholds_k=tk.to(DEV),
+                                thresholds_v=tv.to(DEV), require_fast=True)
+    assert np.array_equal(cache.cpu().numpy(), expect)
+
+
 def test_unsorted_thresholds_use_the_counting_rule():
     heads = 1
     thr = torch.tensor([0.5, 0.1, 0.9, 0.3, 0.7, 0.2, 0.8, 0.4, 0.6, 0.15, 0.25, 0.35, 0.45, 0.55, 0.65], dtype=torch.float16)
