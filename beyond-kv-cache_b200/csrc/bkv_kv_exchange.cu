@@ -4,7 +4,8 @@
 // Every rank attends its own range of positions and is left with one record of un-normalised
 // partials, o (rows x 128) | m (rows, natural log) | l (rows).  The ranks hold a receive buffer
 // each, mapped into all the others through CUDA IPC: [2 parities][world][record] floats followed
-// by [2][world] flag words.  ONE kernel per step then
+// by [2][world] flag words and four control words (steps done, CTAs arrived, two unused).  ONE
+// kernel per step then
 //   1. pushes this rank's record into slot `rank` of every peer's buffer with plain peer stores
 //      (CTA r writes to rank r, one peer at a time), makes it visible system-wide and publishes the
 //      step number in the peer's flag word;
@@ -15,6 +16,9 @@
 // (its own step needs the peer's record), so a slot is never overwritten while it is read.
 // Nothing spins without a limit: when the wait runs out the kernel records it in a status word,
 // leaves the output alone and returns.
+// The step number either comes from the caller (step > 0) or is kept in the rank's own buffer
+// (step = 0): the launch is then the same every time, so a captured graph can replay it.  The CTA
+// that is the last of its grid to finish writes the new count, after every CTA has read the old.
 #include <math_constants.h>
 
 #include <cstring>
@@ -32,7 +36,7 @@ struct ExchangeParams {
   float* peer_recv[kMaxWorld];  // base of every rank's receive buffer (own entry: local pointer)
   int world, rank;
   int64_t rows;
-  int step;                   // > 0, the same on every rank, +1 per call
+  int step;                   // > 0: the same on every rank, +1 per call; 0: counted in the rank's own buffer
   long long timeout_ns;
   void* out;
   int out_dtype;
@@ -55,12 +59,26 @@ __device__ __forceinline__ unsigned long long timer_ns() {
 }
 
 __global__ void __launch_bounds__(kHeadDim) kv_exchange_merge_kernel(const ExchangeParams p) {
-  __shared__ int s_ok;
+  __shared__ int s_ok, s_step;
   pdl_wait();  // launched while the range decode still drains: its record is complete from here on
   const int tid = threadIdx.x;
-  const int parity = p.step & 1;
   const int64_t slot_floats = p.record_floats;
   const int64_t flags_at = 2 * static_cast<int64_t>(p.world) * slot_floats;  // floats before the flag words
+  int* const control = reinterpret_cast<int*>(p.peer_recv[p.rank] + flags_at) + 2 * p.world;  // [steps done, CTAs arrived]
+  if (tid == 0) s_step = p.step > 0 ? p.step : __ldcg(control) + 1;
+  __syncthreads();
+  const int step = s_step;
+  const int parity = step & 1;
+  // (step = 0) every CTA counts itself out; the last one publishes the step for the next launch
+  auto leave = [&] {
+    if (p.step > 0) return;
+    __syncthreads();
+    if (tid == 0 && atomicAdd(control + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      control[1] = 0;
+      __threadfence();
+      atomicExch(control, step);
+    }
+  };
   // ---- 1. push: CTA r delivers this rank's record to rank r ---------------------------------
   for (int r = blockIdx.x; r < p.world; r += gridDim.x) {
     float* const dst = p.peer_recv[r] + (static_cast<int64_t>(parity) * p.world + p.rank) * slot_floats;
@@ -74,7 +92,7 @@ __global__ void __launch_bounds__(kHeadDim) kv_exchange_merge_kernel(const Excha
     __syncthreads();
     if (tid == 0) {
       int* const flag = reinterpret_cast<int*>(p.peer_recv[r] + flags_at) + parity * p.world + p.rank;
-      store_flag(flag, p.step);
+      store_flag(flag, step);
     }
   }
   // ---- 2. wait for every rank's record of this step (bounded) -------------------------------
@@ -84,10 +102,10 @@ __global__ void __launch_bounds__(kHeadDim) kv_exchange_merge_kernel(const Excha
   __syncthreads();
   if (tid < p.world) {
     const unsigned long long t0 = timer_ns();
-    bool ok = load_flag(flags + tid) >= p.step;
+    bool ok = load_flag(flags + tid) >= step;
     unsigned polls = 0;
     while (!ok) {
-      ok = load_flag(flags + tid) >= p.step;
+      ok = load_flag(flags + tid) >= step;
       if (!ok && (++polls & 63u) == 0 && timer_ns() - t0 > static_cast<unsigned long long>(p.timeout_ns)) break;
     }
     if (!ok) s_ok = 0;
@@ -95,6 +113,7 @@ __global__ void __launch_bounds__(kHeadDim) kv_exchange_merge_kernel(const Excha
   __syncthreads();
   if (!s_ok) {
     if (tid == 0) atomicExch(p.status, 1);
+    leave();
     return;
   }
   // ---- 3. merge the records (row = blockIdx.x, thread = dimension) --------------------------
@@ -117,6 +136,7 @@ __global__ void __launch_bounds__(kHeadDim) kv_exchange_merge_kernel(const Excha
     store_out(p.out, row * kHeadDim + tid, p.out_dtype, o);
     if (p.out_f32) p.out_f32[row * kHeadDim + tid] = o;
   }
+  leave();
 }
 
 }  // namespace
@@ -125,7 +145,7 @@ __global__ void __launch_bounds__(kHeadDim) kv_exchange_merge_kernel(const Excha
 extern "C" int64_t bkv_kv_exchange_bytes(int world, int64_t rows) {
   if (world < 1 || world > bkv::kMaxWorld || rows < 0) return 0;
   const int64_t slot = rows * (bkv::kHeadDim + 2);
-  return (2 * world * slot + 2 * world) * 4;
+  return (2 * world * slot + 2 * world + 4) * 4;
 }
 
 extern "C" int bkv_kv_exchange_alloc(int64_t bytes, void** buffer_out, unsigned char* handle64_out) {
@@ -185,7 +205,7 @@ extern "C" int bkv_kv_exchange_merge_sm100(const float* record, int64_t rows, co
                                            float* out_f32, int* status, bkv_stream_t stream) {
   using namespace bkv;
   if (!record || !peer_buffers || !out || !status) return BKV_ERR_ARG;
-  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || rows < 0 || step < 1 || timeout_ns <= 0) return BKV_ERR_ARG;
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || rows < 0 || step < 0 || timeout_ns <= 0) return BKV_ERR_ARG;
   if (out_dtype != BKV_F16 && out_dtype != BKV_BF16 && out_dtype != BKV_F32) return BKV_ERR_ARG;
   if (rows == 0) return BKV_OK;
   if (!aligned16(record)) return BKV_ERR_ALIGN;

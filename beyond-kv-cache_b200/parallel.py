@@ -144,7 +144,6 @@ class KvRangeExchange:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.timeout_ns = int(timeout_s * 1e9)
-        self.step = 0
         self._own = ctypes.c_void_p()
         handle = (ctypes.c_ubyte * 64)()
         with torch.cuda.device(self.device):
@@ -175,9 +174,10 @@ class KvRangeExchange:
 
     def merge(self, out: torch.Tensor, out_f32: Optional[torch.Tensor] = None) -> None:
         """Push this rank's record, wait for the others' and merge into ``out`` (one kernel)."""
-        self.step += 1
+        # step 0: the kernel numbers the steps with a counter in this rank's buffer, so the launch is
+        # the same every time and can be replayed from a captured graph
         _lib.call("bkv_kv_exchange_merge_sm100", self.record.data_ptr(), self.rows, self._peer_array, self.world, self.rank,
-                  self.step, self.timeout_ns, out.data_ptr(), _lib.dtype_code(out.dtype), _lib.ptr(out_f32),
+                  0, self.timeout_ns, out.data_ptr(), _lib.dtype_code(out.dtype), _lib.ptr(out_f32),
                   self.status.data_ptr(), _lib.current_stream(self.device))
 
     def check(self) -> None:
@@ -245,6 +245,7 @@ def decode_kv_range_split(
         q_points_k, q_points_v = q_points_k.float(), q_points_v.float()
     stat = stat_dtype if stat_dtype is not None else q.dtype
     ws = _stream_workspace(q.device)
+    byte_tables = _byte_tables_for(q_points_k, q_points_v, int(layout.num_kv_heads))
     _lib.call(
         "bkv_decode_range_stream_sm100",
         q.data_ptr(), q.stride(0), _lib.dtype_code(q.dtype),
@@ -252,7 +253,7 @@ def decode_kv_range_split(
         int(layout.num_kv_heads), _lib.dtype_code(stat),
         block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
         q_points_k.contiguous().data_ptr(), q_points_v.contiguous().data_ptr(), _lib.dtype_code(q_points_k.dtype),
-        o.data_ptr(), m.data_ptr(), l.data_ptr(), ws.data_ptr(), int(ws.numel()), None, batch, heads_q,
+        o.data_ptr(), m.data_ptr(), l.data_ptr(), ws.data_ptr(), int(ws.numel()), _lib.ptr(byte_tables), batch, heads_q,
         int(token_lo), int(token_hi), float(softmax_scale), 0, 0, _lib.current_stream(q.device),
     )
     if exchange is not None:
@@ -266,3 +267,28 @@ def decode_kv_range_split(
 
 
 _RECORDS: dict = {}
+
+
+def _byte_tables_for(q_points_k: torch.Tensor, q_points_v: torch.Tensor, heads_kv: int) -> Optional[torch.Tensor]:
+    """The decode kernel's expanded look-up tables (128 KiB per kv head) for level tables in the
+    canonical ``(heads_kv * 4, 16)`` order, built on first use and kept on the K tensor for as
+    long as neither tensor is modified.  None (the kernel builds its own, per launch) for tables
+    the builder does not take and while a stream is being captured before the first build."""
+    if q_points_k.dtype not in (torch.float16, torch.bfloat16) or q_points_k.dtype != q_points_v.dtype:
+        return None
+    if tuple(q_points_k.shape) != (heads_kv * 4, 16) or tuple(q_points_v.shape) != (heads_kv * 4, 16):
+        return None
+    if not (q_points_k.is_contiguous() and q_points_v.is_contiguous()):
+        return None
+    held = getattr(q_points_k, "_bkv_range_tables", None)
+    if held is not None and held[0] is q_points_v and held[1] == (q_points_k._version, q_points_v._version):
+        return held[2]
+    if torch.cuda.is_current_stream_capturing():
+        return None
+    with torch.cuda.device(q_points_k.device):
+        nbytes = int(_lib.load().bkv_decode_tables_bytes(heads_kv))
+        tables = torch.empty((nbytes,), dtype=torch.uint8, device=q_points_k.device)
+        _lib.call("bkv_decode_tables_sm100", q_points_k.data_ptr(), q_points_v.data_ptr(), _lib.dtype_code(q_points_k.dtype),
+                  heads_kv, 0, tables.data_ptr(), nbytes, _lib.current_stream(q_points_k.device))
+    q_points_k._bkv_range_tables = (q_points_v, (q_points_k._version, q_points_v._version), tables)
+    return tables

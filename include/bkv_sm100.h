@@ -239,7 +239,10 @@ int bkv_decode_range_stream_sm100(const void* q, int64_t q_batch_stride, int q_d
  * `rank` of every peer's buffer with plain peer stores, publishes `step` in the peer's flag word,
  * waits until the `world` flags of its own buffer show `step`, and merges the records by
  * log-sum-exp into `out` ([rows][128]).  peer_buffers: host array of `world` device addresses,
- * entry `rank` being the own buffer.  step: 1, 2, 3, ... the same sequence on every rank.
+ * entry `rank` being the own buffer.  step: 1, 2, 3, ... the same sequence on every rank, or 0
+ * on every call: the kernel then numbers the steps itself with a counter kept in the rank's own
+ * buffer, which makes the launch identical from step to step (a captured CUDA graph can replay
+ * it); use one of the two forms for the lifetime of a buffer.
  * The wait is bounded: after timeout_ns nanoseconds without the flags the kernel sets *status
  * (device int, never cleared by the library) to 1, leaves `out` untouched and returns; nothing
  * hangs when a peer is gone.  world <= 16.

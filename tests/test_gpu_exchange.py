@@ -54,7 +54,7 @@ def test_two_ranks_in_turn_and_a_wait_that_runs_out():
                                                 token_hi=hi, softmax_scale=synth.softmax_scale(), stat_dtype=torch.bfloat16)
         records.append(torch.cat([o.reshape(-1), m.reshape(-1), l.reshape(-1)]).contiguous())
     nbytes = int(_lib.load().bkv_kv_exchange_bytes(2, rows))
-    assert nbytes == (2 * 2 * rows * 130 + 4) * 4
+    assert nbytes == (2 * 2 * rows * 130 + 4 + 4) * 4  # records, flag words, control words
     bufs = [_alloc(nbytes), _alloc(nbytes)]
     peers = (ctypes.c_uint64 * 2)(bufs[0].value, bufs[1].value)
     try:
@@ -103,6 +103,26 @@ def test_exchange_object_with_one_rank():
                                            stat_dtype=torch.float16, exchange=ex, out_f32=out32)
         ex.check()
         assert np.abs(out32.cpu().numpy() - want).max() <= TOL
+        # the step is counted on the device, so the launches are the same every time: a captured
+        # graph replays range decode + exchange (both buffer parities), here with new queries
+        qd, cd, btd = q.to(DEV), torch.from_numpy(cache).to(DEV), torch.from_numpy(bt).to(DEV)
+        lens_d, lkd, lvd = torch.tensor(lens, dtype=torch.int32, device=DEV), lk.to(DEV), lv.to(DEV)
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.graph(graph, stream=side):
+            parallel.decode_kv_range_split(qd, cd, layout, btd, lens_d, lkd, lvd, out, token_lo=0, token_hi=704,
+                                           softmax_scale=synth.softmax_scale(), stat_dtype=torch.float16, exchange=ex, out_f32=out32)
+        torch.cuda.current_stream().wait_stream(side)
+        for seed in (11, 12, 13):
+            q2 = torch.from_numpy(np.random.default_rng(seed).standard_normal((2, 8, 128)).astype(np.float32)).to(torch.float16)
+            qd.copy_(q2)
+            graph.replay()
+            torch.cuda.synchronize()
+            want2 = oracle.decode_attention(q2.float().numpy(), cache, oracle.PageGeometry(16, 2), bt, lens,
+                                            levels_k=lk.float().numpy(), levels_v=lv.float().numpy(),
+                                            softmax_scale=synth.softmax_scale(), stat="f16")
+            assert np.abs(out32.cpu().numpy() - want2).max() <= TOL
+        ex.check()
         with pytest.raises(ValueError, match="another bucket"):
             parallel.decode_kv_range_split(q.to(DEV)[:1], torch.from_numpy(cache).to(DEV), layout, torch.from_numpy(bt).to(DEV),
                                            torch.tensor(lens, dtype=torch.int32, device=DEV), lk.to(DEV), lv.to(DEV), out[:1],
