@@ -1094,9 +1094,10 @@ __global__ void __maxnreg__(max_regs_for(NW))
       if (!whole) {
         // This part is in place: count its tiles.  The warp whose tiles complete the request merges
         // all its parts (its own included) and writes the result; the others just go on.
-        __threadfence();
+        // (the warp's barrier orders every lane's stores before lane 0's fence: one fence, not thirty-two)
         __syncwarp();
         if (lane == 0) {
+          __threadfence();
           int* const cnt_b = sp.ws_cnt + (static_cast<int64_t>(vh) * B + b);
           if (atomicAdd(cnt_b, kend - k0) + (kend - k0) == nb) {
             *cnt_b = 0;  // nobody else touches it any more: ready for the next launch
@@ -1186,9 +1187,9 @@ __global__ void __maxnreg__(max_regs_for(NW))
       if (!whole) {
         // count this CTA's tiles; the CTA that completes the request merges its parts, every warp
         // taking every NW-th batch of four, and folds the NW results like above
-        __threadfence();
-        __syncthreads();
+        __syncthreads();  // orders every thread's stores before thread 0's fence
         if (tid == 0) {
+          __threadfence();
           int* const cnt_b = sp.ws_cnt + (static_cast<int64_t>(vh) * B + solo_b);
           if (atomicAdd(cnt_b, span) + span == pe - pb) {
             *cnt_b = 0;

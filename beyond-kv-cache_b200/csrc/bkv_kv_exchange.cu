@@ -88,8 +88,7 @@ __global__ void __launch_bounds__(kHeadDim) kv_exchange_merge_kernel(const Excha
     const int64_t n4 = slot_floats % 4 == 0 ? slot_floats / 4 : 0;
     for (int64_t i = tid; i < n4; i += blockDim.x) dst4[i] = src4[i];
     for (int64_t i = n4 * 4 + tid; i < slot_floats; i += blockDim.x) dst[i] = p.record[i];
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // orders every thread's peer stores before the release (system scope) below
     if (tid == 0) {
       int* const flag = reinterpret_cast<int*>(p.peer_recv[r] + flags_at) + parity * p.world + p.rank;
       store_flag(flag, step);
