@@ -947,26 +947,39 @@ __global__ void __maxnreg__(max_regs_for(NW))
       // (no per-tile case analysis: the conditions below are checked once per pair, and everything
       // that fails them - the ends of a run, ragged tails, unmapped pages, short requests - takes
       // the general loop further down, which computes the same values for complete tiles)
-      if (LOADER == 1 && PAIR == 2 && nb > 4) {
+      if (PAIR == 2 && nb > 4) {
         const int k_fast = min(kend, ntok / kTile);  // complete tiles of this part
-        while (k + 2 <= k_fast && run_done + 2 + STAGES <= total && bad_mask == 0 && n_issued - n_done == STAGES) {
+        while (k + 2 <= k_fast && run_done + 2 + STAGES <= total && bad_mask == 0 && n_issued - n_done == STAGES && !dead) {
           const int sB = s + 1 == STAGES ? 0 : s + 1;
-          cp_async_wait_group<STAGES - 1>();
-          __syncwarp();
+          const uint32_t phaseB = s + 1 == STAGES ? phase ^ 1u : phase;
+          if (LOADER == 1) {
+            cp_async_wait_group<STAGES - 1>();
+            __syncwarp();
+          } else if (!wait_full(bar_base + 8 * s, phase)) {
+            dead = true;
+            break;
+          }
           process(std::integral_constant<int, 2>{}, std::false_type{}, ring_base + s * kSlotBytes, ring_base + sB * kSlotBytes,
                   kTile, kTile,
                   [&] {
-                    cp_async_wait_group<STAGES - 2>();
-                    __syncwarp();
+                    if (LOADER == 1) {
+                      cp_async_wait_group<STAGES - 2>();
+                      __syncwarp();
+                    } else if (!wait_full(bar_base + 8 * sB, phaseB)) {
+                      dead = true;
+                    }
                   },
                   [&](int t) {
                     __syncwarp();
+                    if (LOADER != 1) fence_proxy_async();  // reads of the generic proxy before writes of the async proxy
                     issue(run_done + t + STAGES, t ? sB : s);
                   });
+          if (dead) break;
           k += 2;
           run_done += 2;
           n_done += 2;
           s = sB + 1 == STAGES ? 0 : sB + 1;
+          phase = sB + 1 == STAGES ? phaseB ^ 1u : phaseB;
         }
       }
       for (; k < kend;) {
@@ -1002,9 +1015,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
         auto wait_second = [&] { wait_tile(std::integral_constant<int, 1>{}, sB, phaseB); };
         auto refill_tile = [&](int t) { refill(t, t ? sB : s); };
         if (cnt == 2) {
-          if (LOADER != 1 && nvA == kTile && nvB == kTile) {
-            process(std::integral_constant<int, 2>{}, std::false_type{}, sbA, sbB, nvA, nvB, wait_second, refill_tile);
-          } else if (nvA > 0 || nvB > 0) {
+          if (nvA > 0 || nvB > 0) {
             process(std::integral_constant<int, 2>{}, std::true_type{}, sbA, sbB, nvA, nvB, wait_second, refill_tile);
           } else {  // two unmapped pages: nothing to compute, the ring still turns
             wait_second();
