@@ -25,6 +25,9 @@
 // per-(token, group) scale and minimum are applied outside the MMAs:
 //   s[t,h]  = c * sum_g ( scale_k[t,g] * (sum_{d in g} q[h,d] * Lk_g[code_k[t,d]]) + min_k[t,g] * sum_{d in g} q[h,d] )
 //   o[h,d]  = sum_t (p[t,h] * scale_v[t,g(d)]) * Lv_g(d)[code_v[t,d]]  +  sum_t p[t,h] * min_v[t,g(d)]
+// (fp16 statistics: the K-minimum term of s is one more MMA - A = the minima as they lie in the
+// statistic words, B = the per-group sums of q as exact (high, low) fp16 pairs; bf16 statistics
+// use fp32 FMAs.)
 // The queries enter the MMAs un-scaled (a bf16 or fp16 query is exact as an fp16 operand; the
 // softmax scale c is applied to the fp32 score), the probabilities are rounded to fp16 once and
 // the softmax denominator sums the rounded values, so that rounding cancels in the quotient.
@@ -38,6 +41,12 @@
 // A tile that is processed alone (the odd last tile of a request, and every tile of a request of
 // at most four tiles) carries p*scale_v and p*min_v as an exact fp16 (high, low) pair: with a
 // handful of tokens nothing averages the rounding of that product.
+//
+// The steady state - pairs of complete tiles, ring full, a refill behind every tile - is a loop of
+// its own without per-tile case analysis; the ends of a run, ragged tails, unmapped pages and
+// short requests take a general loop that computes the same values.  The per-lane shared-memory
+// offsets of the MMA layouts are kept in registers as opaque values (keep_in_register): left as
+// expressions of the lane index they are recomputed inside the tile loop.
 #include <math_constants.h>
 
 #include <type_traits>
@@ -295,7 +304,7 @@ template <int NW, int STAGES, bool STAT_BF16, int LOADER, int PAIR = 2>
 __global__ void __maxnreg__(max_regs_for(NW))
     decode_stream_kernel(const StreamParams sp, const __grid_constant__ CUtensorMap map_code,
                          const __grid_constant__ CUtensorMap map_stat, const __grid_constant__ CUtensorMap map_vstat) {
-  static_assert(STAGES <= 4, "cp_async_wait_pending handles up to three groups in flight");
+  static_assert(STAGES >= 2 && STAGES <= 4, "a tile pair needs two stages; cp.async groups in flight are counted up to three");
   static_assert(NW * STAGES < kTableBarIndex, "the last barrier word belongs to the byte tables");
   static_assert(4 * NW <= 64, "every warp can be the last of two cut requests in each of the two phases");
   using R = Ring<NW, STAGES>;
@@ -370,7 +379,6 @@ __global__ void __maxnreg__(max_regs_for(NW))
     for (int b = tid; b < B; b += NW * 32) prefix[1 + b] += tot[b >> 5];
     __syncthreads();
   }
-  const int Tb = prefix[B];  // tiles of one head
   // requests without any position to attend are nobody's tiles: their output rows are zeros
   for (int b = cta; b < B; b += C) {
     if (prefix[b + 1] != prefix[b]) continue;

@@ -66,13 +66,6 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait_group() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
-// returns when at most `pending` (0..3) of this thread's newest groups are still in flight
-__device__ __forceinline__ void cp_async_wait_pending(int pending) {
-  if (pending >= 3) cp_async_wait_group<3>();
-  else if (pending == 2) cp_async_wait_group<2>();  // the steady state of a three-stage ring comes first
-  else if (pending == 1) cp_async_wait_group<1>();
-  else cp_async_wait_group<0>();
-}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
