@@ -20,7 +20,9 @@ def test_synthetic_and_default_tables_are_sorted_and_binned():
 def test_tables_the_indexed_look_up_must_not_take():
     _, thr = synth.make_tables(2, seed=1)
     close = thr.clone()
-    close[:, 7] = close[:, 6] + 2.0**-11  # ascending, but two thresholds inside one interval
+    e = torch.floor(close[:, 6].float() * 512)
+    close[:, 6] = ((e + 0.25) / 512).to(close.dtype)  # ascending, but two thresholds inside one interval
+    close[:, 7] = ((e + 0.75) / 512).to(close.dtype)
     assert _tables_sorted(close) and not _tables_binned(close)
     negative = thr.clone()
     negative[:, 0] = -0.125
@@ -42,5 +44,7 @@ def test_tables_the_indexed_look_up_must_not_take():
 def test_the_answer_follows_the_tensor_version():
     _, thr = synth.make_tables(1, seed=2)
     assert _tables_binned(thr)
-    thr[0, 4] = thr[0, 3] + 2.0**-11  # modified in place: the kept answer is stale and must not be used
+    e = float(torch.floor(thr[0, 3].float() * 512))
+    thr[0, 3] = (e + 0.25) / 512  # modified in place: the kept answer is stale and must not be used
+    thr[0, 4] = (e + 0.75) / 512
     assert not _tables_binned(thr)
