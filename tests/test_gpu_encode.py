@@ -209,7 +209,9 @@ def test_tables_with_two_thresholds_in_one_interval_keep_the_search():
     heads, tokens, bs = 2, 5000, 16
     lk, tk, lv, tv = tables(heads, 3)
     tk = tk.clone()
-    tk[:, 7] = tk[:, 6] + 2.0**-11  # sorted, but two thresholds 2^-11 apart
+    e = torch.floor(tk[:, 6].float() * 512)
+    tk[:, 6] = ((e + 0.25) / 512).to(tk.dtype)  # sorted, but two thresholds inside one interval of 2^-9
+    tk[:, 7] = ((e + 0.75) / 512).to(tk.dtype)
     assert _tables_sorted(tk.to(DEV)) and not _tables_binned(tk.to(DEV))
     negative = tv.clone()
     negative[:, 0] = -0.25
