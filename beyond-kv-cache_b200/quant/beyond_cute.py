@@ -382,6 +382,7 @@ def write_tokens_to_paged_cache(
     k_dq_out: Optional[torch.Tensor] = None,
     v_dq_out: Optional[torch.Tensor] = None,
     signal_pdl_dependents: bool = False,
+    wait_for_pdl_predecessor: bool = False,
     require_fast: bool = False,
     stat_dtype: Optional[torch.dtype] = None,
 ) -> None:
@@ -396,6 +397,10 @@ def write_tokens_to_paged_cache(
     this implementation has no fallback and raises ``RuntimeError`` in both cases.
     ``stat_dtype`` (extension) selects fp16/bf16 statistics independently of the input
     dtype; by default statistics use the model dtype as in the reference.
+    ``wait_for_pdl_predecessor`` (extension) launches the writer as a programmatic dependent of
+    the kernel in front of it on the stream: its set-up (tables) runs while that kernel drains and
+    it waits for it before touching rows, slots or the cache - useful behind the kernel that
+    produces K and V, or between the chunks of one long write.
     """
     del block_table, require_fast
     reason = _writer_unsupported_reason(cache, layout, slot_mapping, k, v, k_dq_out, v_dq_out)
@@ -423,6 +428,10 @@ def write_tokens_to_paged_cache(
         common = torch.float32
         qp_k, thr_k, qp_v, thr_v = (t.to(common) for t in (qp_k, thr_k, qp_v, thr_v))
     flags = _lib.FLAG_PDL_TRIGGER if signal_pdl_dependents else 0
+    if wait_for_pdl_predecessor:
+        # the launch may begin while the kernel in front of it on the stream drains; the writer reads
+        # only its tables before it waits for that kernel
+        flags |= _lib.FLAG_PDL_WAIT
     if not (_tables_sorted(thr_k) and _tables_sorted(thr_v)):
         flags |= _lib.FLAG_LINEAR_SEARCH
     elif _tables_binned(thr_k) and _tables_binned(thr_v):

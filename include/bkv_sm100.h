@@ -51,7 +51,12 @@ extern "C" {
 #define BKV_FLAG_PDL_WAIT 0x2      /* decode: launched as a programmatic dependent of the
                                       immediately preceding kernel, which must be the cache
                                       writer: sequence lengths, block table and queries are
-                                      read before the wait and must come from older launches */
+                                      read before the wait and must come from older launches.
+                                      encode: likewise launched as a programmatic dependent of
+                                      whatever kernel precedes it on the stream; only the
+                                      threshold / level tables are read before the wait (rows,
+                                      slots and cache after it), so the predecessor may be the
+                                      producer of K and V or an earlier chunk of the same write */
 #define BKV_FLAG_LINEAR_SEARCH 0x4 /* encode: count thresholds linearly (unsorted tables) */
 #define BKV_FLAG_KLEVELS_LANE_MAJOR 0x8 /* decode: K levels given as (Hkv,16,4)      */
 #define BKV_FLAG_BINNED_TABLES 0x10 /* encode: the caller has checked, for both threshold tensors,

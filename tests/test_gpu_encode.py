@@ -168,7 +168,8 @@ def test_large_writes_with_classified_tables(kind, table_dtype, heads, shared):
     from beyond_kv_cache_b200.quant.beyond_cute import _tables_binned
 
     rng = np.random.default_rng(41 + heads)
-    tokens, bs = 6000, 16
+    # (the indexed form takes writes of 96 tokens per SM and more)
+    tokens, bs = 96 * torch.cuda.get_device_properties(0).multi_processor_count + 300, 16
     dt = KIND_TO_DTYPE[kind]
     lk, tk, lv, tv = tables(heads, 9, per_group=not shared)
     if shared:
@@ -203,10 +204,38 @@ def test_large_writes_with_classified_tables(kind, table_dtype, heads, shared):
         assert np.array_equal(bits16(got), bits16(torch.from_numpy(want).to(dt)))  # slot -1 rows too
 
 
+@pytest.mark.parametrize("chunk", [15000, 8192, 1000])
+def test_chunks_chained_as_programmatic_dependents(chunk):
+    """One long write issued as chunks on one stream, every chunk signalling its dependents early and
+    launched as a programmatic dependent of the chunk in front (both the indexed and the searching
+    form, by chunk size): the same page bytes as the oracle's single write."""
+    heads, bs, tokens = 8, 16, 3 * chunk + 77
+    rng = np.random.default_rng(chunk)
+    lk, tk, lv, tv = (t.to(DEV) for t in tables(heads, 11))
+    k = torch.from_numpy(rng.standard_normal((tokens, heads, 128)).astype(np.float32)).to(torch.bfloat16)
+    v = torch.from_numpy((rng.standard_normal((tokens, heads, 128)) * 2).astype(np.float32)).to(torch.bfloat16)
+    geo = oracle.PageGeometry(bs, heads, 128)
+    pages = tokens // bs + 3
+    seed_pages = rng.integers(-(2**31), 2**31, (pages, geo.block_i32)).astype(np.int32)
+    slots = rng.permutation(pages * bs)[:tokens].astype(np.int64)
+    expect = seed_pages.copy()
+    oracle.write_pages(expect, geo, slots, k.float().numpy(), v.float().numpy(), thresholds_k=tk.float().cpu().numpy(),
+                       thresholds_v=tv.float().cpu().numpy(), stat="bf16")
+    cache = torch.from_numpy(seed_pages).to(DEV)
+    kd, vd, sd = k.to(DEV), v.to(DEV), torch.from_numpy(slots).to(DEV)
+    layout = PagedLayout.build_hnd(bs, heads, 128, 4, 32, 32)
+    for c0 in range(0, tokens, chunk):
+        write_tokens_to_paged_cache(cache, layout, None, sd[c0:c0 + chunk], kd[c0:c0 + chunk], vd[c0:c0 + chunk],
+                                    q_points_k=lk, q_points_v=lv, thresholds_k=tk, thresholds_v=tv, require_fast=True,
+                                    signal_pdl_dependents=True, wait_for_pdl_predecessor=c0 > 0)
+    torch.cuda.synchronize()
+    assert np.array_equal(cache.cpu().numpy(), expect)
+
+
 def test_tables_with_two_thresholds_in_one_interval_keep_the_search():
     from beyond_kv_cache_b200.quant.beyond_cute import _tables_binned, _tables_sorted
 
-    heads, tokens, bs = 2, 5000, 16
+    heads, tokens, bs = 2, 96 * torch.cuda.get_device_properties(0).multi_processor_count + 100, 16
     lk, tk, lv, tv = tables(heads, 3)
     tk = tk.clone()
     e = torch.floor(tk[:, 6].float() * 512)
