@@ -513,6 +513,15 @@ __global__ void __maxnreg__(max_regs_for(NW))
     const int wa = part::run_begin(sh, NW, warp), wb = part::run_begin(sh, NW, warp + 1);
     const int total = wb - wa;
     const bool work = total > 0 && !dead;
+    // The CTA's first head: nothing reads the table space yet, so the two bulk copies of its byte
+    // tables are requested before the page ids and the first ring fill instead of behind them.
+    if (ph == 0 && sp.byte_tables && tid == 0) {
+      const uint32_t bar = kFullBar + 8 * kTableBarIndex;
+      mbar_arrive_expect_tx(bar, 2 * kLutBlock);
+      const char* const src = reinterpret_cast<const char*>(sp.byte_tables) + static_cast<int64_t>(head) * (2 * kLutBlock);
+      bulk_copy_g2s(kLutAddr, src, kLutBlock, bar);
+      bulk_copy_g2s(kLutAddr + kLutBlock, src + kLutBlock, kLutBlock, bar);
+    }
     // this head's level tables: requested now, stored to shared memory after the first ring fill
     // has been issued, so the read overlaps the page-id read below
     float level_early = 0.f;
@@ -627,7 +636,7 @@ __global__ void __maxnreg__(max_regs_for(NW))
     if (sp.byte_tables) {
       // the two table blocks of this head were laid out once per layer: two bulk copies
       const uint32_t bar = kFullBar + 8 * kTableBarIndex;
-      if (tid == 0) {
+      if (tid == 0 && ph != 0) {
         fence_proxy_async();  // the reads of the old tables before the writes of the copy unit
         mbar_arrive_expect_tx(bar, 2 * kLutBlock);
         const char* const src = reinterpret_cast<const char*>(sp.byte_tables) + static_cast<int64_t>(head) * (2 * kLutBlock);
