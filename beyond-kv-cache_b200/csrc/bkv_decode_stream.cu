@@ -1479,13 +1479,19 @@ void plan_launch(int hv, int batch, int max_seq_len, int sm_count, part::Plan* p
   const int base = C / hv;
   const double per_cta_us = static_cast<double>(tiles_max) / C * 0.1;
   const double aligned_loss_us = per_cta_us * (static_cast<double>(C) / hv / base - 1.0);
-  // compensated equal shares lose about (heads - 1) gaps spread over all CTAs
-  const double equal_loss_us = 4.0 * (hv - 1) / C + 1.0;
+  // A CTA whose share straddles two heads drains its rings, waits for its warps, brings in the
+  // second head's 128 KiB of tables and restarts its pipelines: about 12 us, i.e. the time of 160
+  // tiles, by which its share is shortened (per-CTA time stamps on batch 64 x 8 K: with 40 the four
+  // straddling CTAs finished 7 us behind the median and set the end of the kernel; 160 to 250
+  // measure alike, 149 against 155 us per step).  Compensated equal shares lose about
+  // (heads - 1) such gaps spread over all CTAs.
+  constexpr int kStraddleTiles = 160;
+  const double equal_loss_us = 0.08 * kStraddleTiles * (hv - 1) / C + 1.0;
   pl->C = C;
   pl->NW = NW;
   pl->hv = hv;
   pl->Tb = 0;  // known on the device only
-  pl->gap = 40;  // ~4 us: with 100 the straddling CTAs were measured to finish 7 us early
+  pl->gap = kStraddleTiles;
   pl->aligned = (C % hv == 0 || aligned_loss_us < equal_loss_us) ? 1 : 0;
 }
 
